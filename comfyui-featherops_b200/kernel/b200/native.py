@@ -1,0 +1,321 @@
+"""ctypes binding of libfeather_b200.so, the C-ABI library declared in include/feather_b200.h.
+
+This is the only place the Python side touches native code.  PyTorch is used for device memory and streams only:
+every call passes raw device pointers and the current CUDA stream of the tensors' device.  There is no CPU or
+PyTorch fallback: if the library is missing, or a tensor is not on a CUDA device, the call raises.
+
+Stands in for kernel/hip/utils.py:67-129 (`load_hip_stable_extension`) of the reference, which JIT-builds and
+loads the HIP extension.
+"""
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+LIB_PATH = os.path.join(_PKG_DIR, "libfeather_b200.so")
+
+FEATHER_OK = 0
+FEATHER_ERR_DEVICE_TIMEOUT = 5
+OUT_FP16, OUT_BF16 = 0, 1
+SRC_FP32, SRC_BF16, SRC_FP16 = 0, 1, 2
+
+_SRC_CODE = {torch.float32: SRC_FP32, torch.bfloat16: SRC_BF16, torch.float16: SRC_FP16}
+_OUT_CODE = {torch.float16: OUT_FP16, torch.bfloat16: OUT_BF16}
+
+EXPORTED_SYMBOLS = (
+    "launch_scaled_mm",
+    "feather_scaled_mm_ex",
+    "feather_scaled_mm_workspace_bytes",
+    "feather_scaled_mm_choose",
+    "feather_quantize_prepack",
+    "feather_prepack_bytes",
+    "feather_unprepack_bytes",
+    "feather_dequantize",
+    "feather_bf16_to_fp16",
+    "feather_last_error_string",
+    "feather_version",
+)
+
+
+class MMVariant(ctypes.Structure):
+    """Mirror of `feather_mm_variant`; all-zero means "library chooses"."""
+
+    _fields_ = [
+        ("tokens_tile", ctypes.c_int),
+        ("cta_pair", ctypes.c_int),
+        ("split_k", ctypes.c_int),
+        ("transform_groups", ctypes.c_int),
+        ("max_ctas", ctypes.c_int),
+    ]
+
+    def as_tuple(self):
+        return (self.tokens_tile, self.cta_pair, self.split_k, self.transform_groups, self.max_ctas)
+
+
+class FeatherNativeError(RuntimeError):
+    pass
+
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def load_library():
+    """Load (once) and return the ctypes handle.  Raises if the library has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lib_lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise FeatherNativeError(
+                f"{LIB_PATH} is missing. Build it with `python {os.path.join(_PKG_DIR, 'build.py')}` "
+                "(needs nvcc; there is no fallback implementation)."
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        vp, i64, ci, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+        lib.launch_scaled_mm.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, ci, ci, ci, ci, ci, vp]
+        lib.launch_scaled_mm.restype = ci
+        lib.feather_scaled_mm_ex.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, sz, vp, vp]
+        lib.feather_scaled_mm_ex.restype = ci
+        lib.feather_scaled_mm_workspace_bytes.argtypes = [i64, i64, i64, ctypes.POINTER(MMVariant)]
+        lib.feather_scaled_mm_workspace_bytes.restype = sz
+        lib.feather_scaled_mm_choose.argtypes = [i64, i64, i64, sz, ctypes.POINTER(MMVariant)]
+        lib.feather_scaled_mm_choose.restype = ci
+        lib.feather_quantize_prepack.argtypes = [vp, ci, vp, i64, i64, ci, vp, vp, vp, vp]
+        lib.feather_quantize_prepack.restype = ci
+        lib.feather_prepack_bytes.argtypes = [vp, i64, i64, ci, vp, vp]
+        lib.feather_prepack_bytes.restype = ci
+        lib.feather_unprepack_bytes.argtypes = [vp, i64, i64, vp, vp]
+        lib.feather_unprepack_bytes.restype = ci
+        lib.feather_dequantize.argtypes = [vp, vp, i64, i64, ci, vp, vp]
+        lib.feather_dequantize.restype = ci
+        lib.feather_bf16_to_fp16.argtypes = [vp, vp, i64, vp]
+        lib.feather_bf16_to_fp16.restype = ci
+        lib.feather_last_error_string.argtypes = []
+        lib.feather_last_error_string.restype = ctypes.c_char_p
+        lib.feather_version.argtypes = []
+        lib.feather_version.restype = ci
+        _lib = lib
+    return _lib
+
+
+def _check(status, what):
+    if status != FEATHER_OK:
+        msg = load_library().feather_last_error_string().decode("utf-8", "replace")
+        raise FeatherNativeError(f"{what} failed (status {status}): {msg}")
+
+
+def _require_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise FeatherNativeError("FeatherOps B200 kernels need CUDA tensors; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise FeatherNativeError("all tensors must be on the same CUDA device")
+    return dev
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+# ------------------------------------------------------------------------------------------------
+# Per-device scratch owned by the Python side (the C ABI never allocates).
+# ------------------------------------------------------------------------------------------------
+_WORKSPACE_BYTES = 64 << 20   # split-K partials; covers every shape in the shipped heuristics
+_scratch_lock = threading.Lock()
+_workspaces = {}
+_status_words = {}
+_amax_words = {}
+
+
+def workspace_for(device):
+    """Zero-initialised split-K workspace of `device` (allocated on first use through torch's allocator).
+
+    The kernel leaves the tile counters at the start of the workspace at zero after every launch, so one buffer
+    serves every later call on the same stream.
+    """
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    with _scratch_lock:
+        ws = _workspaces.get(key)
+        if ws is None:
+            ws = torch.zeros(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
+        return ws
+
+
+def status_word_for(device):
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    with _scratch_lock:
+        st = _status_words.get(key)
+        if st is None:
+            st = torch.zeros(1, dtype=torch.int32, device=device)
+            _status_words[key] = st
+        return st
+
+
+def _amax_word_for(device):
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    with _scratch_lock:
+        w = _amax_words.get(key)
+        if w is None:
+            w = torch.zeros(2, dtype=torch.int32, device=device)
+            _amax_words[key] = w
+        return w
+
+
+def check_device_status(device=None):
+    """Synchronise `device` and raise if a kernel recorded a failure (a bounded wait that ran out).
+
+    The hot path never calls this (it would serialise the stream); tests and debugging do.
+    """
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    st = status_word_for(device)
+    value = int(st.item())
+    if value != 0:
+        st.zero_()
+        role = (value >> 8) & 0xFF
+        detail = (value >> 16) & 0xFFFF
+        names = {1: "TMA producer", 2: "MMA issuer", 3: "transform warp", 4: "epilogue warp"}
+        raise FeatherNativeError(
+            f"scaled_mm kernel reported status {value & 0xFF} ({names.get(role, 'role ' + str(role))}, detail 0x{detail:x}): "
+            "a bounded wait ran out and the kernel returned early; the output is not valid"
+        )
+
+
+# ------------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------------
+def make_variant(tokens_tile=0, cta_pair=0, split_k=0, transform_groups=0, max_ctas=0):
+    return MMVariant(tokens_tile, cta_pair, split_k, transform_groups, max_ctas)
+
+
+def choose_variant(M, N, K, workspace_bytes=_WORKSPACE_BYTES):
+    v = MMVariant()
+    _check(load_library().feather_scaled_mm_choose(M, N, K, workspace_bytes, ctypes.byref(v)), "feather_scaled_mm_choose")
+    return v
+
+
+def workspace_bytes(M, N, K, variant=None):
+    return int(load_library().feather_scaled_mm_workspace_bytes(M, N, K, ctypes.byref(variant) if variant is not None else None))
+
+
+def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
+    """c[:, :N] = cvt((a @ up(b)) * scale) + bias on the current stream of a's device.  No allocation, no sync.
+
+    `c` may be a column slice of a wider row-major buffer (stride(0) >= N, stride(1) == 1): that is how a weight
+    shard writes its block of columns in place.
+    """
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, c)
+    M, K = a.shape
+    N = b_prepacked.shape[1] if n_cols is None else n_cols
+    ws = workspace_for(dev)
+    st = status_word_for(dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_scaled_mm_ex(
+            _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c),
+            M, N, K, c.stride(0), _OUT_CODE[c.dtype],
+            ctypes.byref(variant) if variant is not None else None,
+            _ptr(ws), ws.numel(), _ptr(st), _stream_ptr(dev),
+        )
+    _check(status, "feather_scaled_mm_ex")
+    return c
+
+
+def launch_scaled_mm_reference_abi(a, b_prepacked, scale, bias, c, cfg=(1, 8, 4, 8, 2), b_dtype=1):
+    """Calls the entry point that keeps the reference's `launch_scaled_mm` argument order. Returns its int result."""
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, c)
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    with torch.cuda.device(dev):
+        return lib.launch_scaled_mm(
+            _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), M, N, K,
+            1 if scale is not None else 0, 1 if bias is not None else 0, *cfg, b_dtype, _OUT_CODE[c.dtype], _stream_ptr(dev),
+        )
+
+
+# ------------------------------------------------------------------------------------------------
+# Weight format
+# ------------------------------------------------------------------------------------------------
+def quantize_prepack(src, scale=None, premul=None):
+    """src [N,K] fp32/bf16/fp16 (contiguous, CUDA) -> (qdata e5m2 [K/16,N,16], scale fp32 0-dim).
+
+    scale=None recalculates amax/57344 (with the reference's zero and fp16-clamp rules); otherwise `scale` is a
+    fp32 CUDA tensor with one element that is used as given.  premul (fp32, one element) multiplies an fp32 source first.
+    """
+    lib = load_library()
+    dev = _require_cuda(src, scale, premul)
+    N, K = src.shape
+    qdata = torch.empty((K // 16, N, 16), dtype=torch.float8_e5m2, device=dev)
+    recalc = scale is None
+    scale_io = torch.empty((), dtype=torch.float32, device=dev) if recalc else scale.reshape(()).to(torch.float32).clone()
+    with torch.cuda.device(dev):
+        status = lib.feather_quantize_prepack(
+            _ptr(src), _SRC_CODE[src.dtype], _ptr(premul), N, K, 1 if recalc else 0, _ptr(scale_io), _ptr(_amax_word_for(dev)),
+            _ptr(qdata), _stream_ptr(dev),
+        )
+    _check(status, "feather_quantize_prepack")
+    return qdata, scale_io
+
+
+def prepack_bytes(src, src_is_kn=False):
+    """e5m2/uint8 [N,K] (or [K,N] when src_is_kn) -> [K/16,N,16], same dtype."""
+    lib = load_library()
+    dev = _require_cuda(src)
+    if src_is_kn:
+        K, N = src.shape
+    else:
+        N, K = src.shape
+    dst = torch.empty((K // 16, N, 16), dtype=src.dtype, device=dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_prepack_bytes(_ptr(src), N, K, 1 if src_is_kn else 0, _ptr(dst), _stream_ptr(dev))
+    _check(status, "feather_prepack_bytes")
+    return dst
+
+
+def unprepack_bytes(src):
+    lib = load_library()
+    dev = _require_cuda(src)
+    kb, N, _ = src.shape
+    dst = torch.empty((N, kb * 16), dtype=src.dtype, device=dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_unprepack_bytes(_ptr(src), N, kb * 16, _ptr(dst), _stream_ptr(dev))
+    _check(status, "feather_unprepack_bytes")
+    return dst
+
+
+def dequantize(src_prepacked, scale, dtype):
+    lib = load_library()
+    dev = _require_cuda(src_prepacked, scale)
+    kb, N, _ = src_prepacked.shape
+    dst = torch.empty((N, kb * 16), dtype=dtype, device=dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_dequantize(_ptr(src_prepacked), _ptr(scale), N, kb * 16, _SRC_CODE[dtype], _ptr(dst), _stream_ptr(dev))
+    _check(status, "feather_dequantize")
+    return dst
+
+
+def bf16_to_fp16(x):
+    lib = load_library()
+    dev = _require_cuda(x)
+    out = torch.empty_like(x, dtype=torch.float16)
+    with torch.cuda.device(dev):
+        status = lib.feather_bf16_to_fp16(_ptr(x), _ptr(out), x.numel(), _stream_ptr(dev))
+    _check(status, "feather_bf16_to_fp16")
+    return out

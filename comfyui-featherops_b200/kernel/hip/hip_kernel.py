@@ -1,0 +1,166 @@
+"""Operator surface of the mixed-precision linear, same names and signatures as the reference's
+kernel/hip/hip_kernel.py (the module path is kept so `comfy_feather/ops.py` and the reference's test and benchmark
+scripts import it unchanged), routed to the sm_100a library instead of the HIP extension.
+
+    scaled_mm_hip(a, b_prepacked, scale, bias, out_dtype)                      hip_kernel.py:136-167
+    scaled_mm_hip_configured(a, b_prepacked, scale, bias, out_dtype, *cfg5)    hip_kernel.py:12-58
+    _CONFIGS                                                                   hip_kernel.py:60-93
+    prepack_b_for_scaled_mm(b)                                                 hip_kernel.py:170-171
+    torch.ops.feather_ops.scaled_mm(a, b, scale, bias, c, 5 ints, b_dtype)     hip_kernel.cu:746-767
+
+Differences a caller can observe: the five tile integers are accepted and ignored (the kernel variant is chosen from
+the shape, so there is no first-call autotune pause); M does not have to be a multiple of any tile (ragged token counts
+are handled in the kernel); fp8e4m3 weights are rejected.
+"""
+
+import torch
+
+from ..b200 import native
+
+# The reference's 28 tile configs, kept so scripts that iterate `_CONFIGS` keep working.  (warps_m, warps_n,
+# unroll_k, repeat_m, repeat_n); every entry maps to the same shape-driven variant here.
+_CONFIGS = sorted(
+    [
+        (1, 1, 2, 1, 2), (1, 1, 4, 1, 2), (1, 2, 2, 1, 2), (1, 2, 4, 1, 2), (1, 4, 2, 1, 2), (1, 4, 4, 1, 2), (1, 8, 2, 1, 2),
+        (1, 8, 4, 1, 2), (1, 1, 2, 2, 2), (1, 1, 4, 2, 2), (1, 1, 2, 4, 4), (1, 1, 4, 4, 4), (1, 2, 2, 2, 2), (1, 2, 4, 2, 2),
+        (2, 1, 2, 2, 2), (2, 1, 4, 2, 2), (1, 4, 2, 4, 2), (1, 4, 4, 4, 2), (1, 8, 2, 8, 2), (1, 8, 4, 8, 2), (2, 2, 2, 4, 4),
+        (2, 2, 4, 4, 4), (2, 4, 2, 4, 2), (2, 4, 4, 4, 2), (2, 4, 2, 4, 4), (2, 4, 4, 4, 4), (4, 2, 2, 2, 4), (4, 2, 4, 2, 4),
+    ],
+    key=lambda x: (x[0], x[1], x[3], x[4], x[2]),
+)  # fmt: skip
+
+
+def _check(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _validate(a, b_prepacked, scale, bias, c, b_dtype):
+    """Argument checks of the reference op (hip_kernel.cu:648-730), minus tile divisibility of M and N."""
+    _check(a.is_cuda, "a must be a CUDA tensor")
+    _check(b_prepacked.is_cuda, "b_prepacked must be a CUDA tensor")
+    _check(c.is_cuda, "c must be a CUDA tensor")
+    _check(b_prepacked.device == a.device, "b_prepacked must be on the same device as a")
+    _check(c.device == a.device, "c must be on the same device as a")
+    _check(a.dtype == torch.float16, "a must be float16")
+    _check(c.dtype in (torch.float16, torch.bfloat16), "c must be float16 or bfloat16")
+    _check(b_dtype in (0, 1), "b_dtype must be 0 (fp8e4m3) or 1 (fp8e5m2)")
+    _check(b_dtype == 1, "fp8e4m3 weights are not supported by the sm_100a kernel; b_dtype must be 1 (fp8e5m2)")
+    _check(b_prepacked.dtype == torch.float8_e5m2, "b_prepacked must be float8_e5m2 when b_dtype=1")
+    _check(a.dim() == 2, "a must be 2D")
+    _check(b_prepacked.dim() == 3, "b_prepacked must be 3D (K/16, N, 16)")
+    _check(c.dim() == 2, "c must be 2D")
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    _check(K % 16 == 0, "K must be divisible by 16")
+    _check(b_prepacked.shape[0] == K // 16, f"b_prepacked.shape[0] must equal K/16 ({K // 16})")
+    _check(b_prepacked.shape[2] == 16, "b_prepacked.shape[2] must be 16")
+    _check(c.shape[0] == M, "c.shape[0] must equal M")
+    _check(c.shape[1] == N, "c.shape[1] must equal N")
+    _check(a.stride(0) == K or M <= 1, f"a.stride(0) must equal K ({K})")
+    _check(a.stride(1) == 1, "a.stride(1) must be 1")
+    _check(b_prepacked.stride(0) == N * 16 or K == 16, f"b_prepacked.stride(0) must equal N*16 ({N * 16})")
+    _check(b_prepacked.stride(1) == 16, "b_prepacked.stride(1) must be 16")
+    _check(b_prepacked.stride(2) == 1, "b_prepacked.stride(2) must be 1")
+    _check(c.stride(0) >= N or M <= 1, f"c.stride(0) must be at least N ({N})")
+    _check(c.stride(1) == 1, "c.stride(1) must be 1")
+    if scale is not None:
+        _check(scale.is_cuda, "scale must be a CUDA tensor")
+        _check(scale.device == a.device, "scale must be on the same device as a")
+        _check(scale.dtype == torch.float32, "scale must be float32")
+        _check(scale.numel() == 1, "scale must have one element")
+    if bias is not None:
+        _check(bias.is_cuda, "bias must be a CUDA tensor")
+        _check(bias.device == a.device, "bias must be on the same device as a")
+        _check(bias.dtype == c.dtype, "bias must have the same dtype as c")
+        _check(bias.numel() == N, "bias must have N elements")
+        _check(bias.is_contiguous(), "bias must be contiguous")
+    _check(a.data_ptr() % 16 == 0, "a data pointer must be 16-byte aligned")
+    _check(b_prepacked.data_ptr() % 16 == 0, "b_prepacked data pointer must be 16-byte aligned")
+
+
+# ------------------------------------------------------------------------------------------------
+# torch.ops.feather_ops.scaled_mm: same schema as the reference's stable-ABI op (out-parameter convention).
+# ------------------------------------------------------------------------------------------------
+_lib_def = torch.library.Library("feather_ops", "DEF")
+_lib_def.define(
+    "scaled_mm(Tensor a, Tensor b_prepacked, Tensor? scale, Tensor? bias, Tensor(a!) c, int block_warps_m, int block_warps_n, "
+    "int unroll_k, int repeat_m, int repeat_n, int b_dtype) -> ()"
+)
+
+
+def _scaled_mm_cuda(a, b_prepacked, scale, bias, c, block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n, b_dtype):
+    _validate(a, b_prepacked, scale, bias, c, b_dtype)
+    if a.shape[0] == 0:
+        return
+    native.scaled_mm_into(a, b_prepacked, scale, bias, c)
+
+
+_lib_impl = torch.library.Library("feather_ops", "IMPL")
+_lib_impl.impl("scaled_mm", _scaled_mm_cuda, "CUDA")
+
+
+def _scaled_mm_meta(a, b_prepacked, scale, bias, c, block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n, b_dtype):
+    return None
+
+
+_lib_impl.impl("scaled_mm", _scaled_mm_meta, "Meta")
+
+
+@torch.library.custom_op("feather_ops_internal::scaled_mm_configured", mutates_args=())
+def _configured_op(
+    a: torch.Tensor,
+    b_prepacked: torch.Tensor,
+    scale: torch.Tensor | None,
+    bias: torch.Tensor | None,
+    out_dtype: torch.dtype,
+    block_warps_m: int,
+    block_warps_n: int,
+    unroll_k: int,
+    repeat_m: int,
+    repeat_n: int,
+) -> torch.Tensor:
+    out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
+    torch.ops.feather_ops.scaled_mm.default(
+        a, b_prepacked, scale, bias, out, block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n,
+        0 if b_prepacked.dtype == torch.float8_e4m3fn else 1,
+    )  # fmt: skip
+    return out
+
+
+@_configured_op.register_fake
+def _(a, b_prepacked, scale, bias, out_dtype, block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n):
+    return torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
+
+
+scaled_mm_hip_configured = _configured_op
+
+_DEFAULT_CFG = (1, 8, 4, 8, 2)
+
+
+def scaled_mm_hip(
+    a: torch.Tensor,
+    b_prepacked: torch.Tensor,
+    scale: torch.Tensor | None,
+    bias: torch.Tensor | None,
+    out_dtype: torch.dtype,
+) -> torch.Tensor:
+    """C = cvt((a @ up(b_prepacked)) * scale) + bias.  a fp16 [M,K]; b_prepacked e5m2 [K/16,N,16]; returns [M,N].
+
+    Under torch.compile the call stays one opaque custom op (with a fake implementation for shape inference);
+    in eager mode it validates, allocates the output and launches, with no autotune step.
+    """
+    if torch.compiler.is_compiling():
+        return _configured_op(a, b_prepacked, scale, bias, out_dtype, *_DEFAULT_CFG)
+    out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
+    _scaled_mm_cuda(a, b_prepacked, scale, bias, out, *_DEFAULT_CFG, 0 if b_prepacked.dtype == torch.float8_e4m3fn else 1)
+    return out
+
+
+def prepack_b_for_scaled_mm(b: torch.Tensor) -> torch.Tensor:
+    """(K, N) -> (K/16, N, 16): out[kb, n, j] = b[16*kb + j, n]."""
+    if b.dim() != 2 or b.shape[0] % 16 != 0:
+        raise RuntimeError("b must be 2D (K, N) with K divisible by 16")
+    if b.element_size() != 1:
+        raise RuntimeError("prepack_b_for_scaled_mm expects an 8-bit weight tensor")
+    return native.prepack_bytes(b.contiguous(), src_is_kn=True)

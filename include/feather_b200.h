@@ -1,0 +1,149 @@
+/*
+ * feather_b200.h - C ABI of libfeather_b200.so (sm_100a).
+ *
+ * The library is the native side of the FeatherOps mixed-precision linear:
+ *     C[M,N] = cvt( (A[M,K] fp16 . up(W[K,N] fp8e5m2)) * scale ) + bias        fp32 accumulate
+ * with W stored prepacked as (K/16, N, 16) bytes, plus the quantise-and-prepack that produces W.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless its name ends in _host
+ *   - pointers are borrowed: the caller keeps the memory alive until the stream work has finished
+ *   - work is enqueued on `stream`; nothing here synchronises the device
+ *   - no entry point allocates device memory (scratch is passed in by the caller); none throws
+ *   - the return value is a feather_status (0 = ok).  Device-side failures (a bounded wait inside a
+ *     kernel that ran out) are written to the optional `status_dev` word and are visible to the host
+ *     after the stream has been synchronised.
+ *
+ * Each declaration cites the interface of the reference (woct0rdho/ComfyUI-FeatherOps) it stands in
+ * for, as path:line inside that project.
+ */
+#ifndef FEATHER_B200_H_
+#define FEATHER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FEATHER_API __attribute__((visibility("default")))
+#else
+#define FEATHER_API
+#endif
+
+/* CUDA stream handle (cudaStream_t) passed as an opaque pointer so this header needs no CUDA include. */
+typedef void* feather_stream_t;
+
+typedef enum feather_status {
+    FEATHER_OK = 0,
+    FEATHER_ERR_BAD_ARGUMENT = 1,    /* null pointer, negative size, K % 16 != 0, misaligned pointer ... */
+    FEATHER_ERR_UNSUPPORTED = 2,     /* e.g. b_dtype = fp8e4m3, unknown kernel variant */
+    FEATHER_ERR_WORKSPACE = 3,       /* variant needs more scratch than was passed */
+    FEATHER_ERR_CUDA = 4,            /* a CUDA runtime / driver call failed; see feather_last_error_string */
+    FEATHER_ERR_DEVICE_TIMEOUT = 5,  /* value found in *status_dev after a kernel gave up on a bounded wait */
+    FEATHER_ERR_NO_DEVICE = 6        /* no sm_100 device / driver entry point unavailable */
+} feather_status;
+
+/* Weight / output dtype codes, same numbering as kernel/hip/hip_kernel.cu:579-580 */
+enum { FEATHER_B_E4M3 = 0, FEATHER_B_E5M2 = 1 };
+enum { FEATHER_OUT_FP16 = 0, FEATHER_OUT_BF16 = 1 };
+/* Source dtype codes of the quantiser */
+enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
+
+/* Kernel variant selection for feather_scaled_mm_ex.  All fields 0 = let the library choose.
+ *   tokens_tile : activation rows per MMA tile (the MMA N extent): 16, 32, 64, 128 or 256
+ *   cta_pair    : 1 = one CTA per tile (128 weight columns), 2 = two-CTA pairs (256 weight columns)
+ *   split_k     : number of K slices reduced through the fp32 workspace (1 = none)
+ *   transform_groups : groups of four warps that upcast e5m2 weight stages (1 or 2)
+ *   max_ctas    : cap on the persistent grid (0 = number of SMs)
+ */
+typedef struct feather_mm_variant {
+    int tokens_tile;
+    int cta_pair;
+    int split_k;
+    int transform_groups;
+    int max_ctas;
+} feather_mm_variant;
+
+/* ---------------------------------------------------------------------------------------------
+ * GEMM
+ * ------------------------------------------------------------------------------------------- */
+
+/* Drop-in for `extern "C" bool launch_scaled_mm(...)`, kernel/hip/hip_kernel.cu:564-582: same argument
+ * order and meaning, cudaStream_t in place of hipStream_t.  The five tile integers are accepted and
+ * ignored (the variant is chosen from the shape); b_dtype must be 1 (e5m2).  Returns 1 when the launch
+ * was enqueued, 0 otherwise (the reference returns false for an unknown config).  This entry point
+ * takes no workspace, so it never uses a split-K variant. */
+FEATHER_API int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
+                     int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, int block_warps_m, int block_warps_n,
+                     int unroll_k, int repeat_m, int repeat_n, int b_dtype, int output_dtype, feather_stream_t stream);
+
+/* Full form used by the Python operator (kernel/hip/hip_kernel.py:12-39 `_configured_op` ->
+ * `torch.ops.feather_ops.scaled_mm`, kernel/hip/hip_kernel.cu:635-744).
+ *   a            fp16 [M,K] row-major, 16-byte aligned
+ *   b_prepacked  e5m2 bytes [K/16, N, 16], 16-byte aligned
+ *   scale        fp32[1] or NULL; bias  out-dtype [N] or NULL
+ *   c            out-dtype [M, ldc] row-major; only columns [0,N) of each row are written.  ldc >= N
+ *                lets a column shard write straight into its slice of a wider output.
+ *   workspace    scratch for split-K variants (may be NULL), 16-byte aligned.  It must be zero-filled
+ *                once after allocation (tile counters live at its start); every launch that completes
+ *                leaves the counters at zero again, so the same buffer serves any later call.
+ *                Two launches that may overlap on the device need separate workspaces.
+ *   status_dev   int32 device word or NULL; left untouched on success
+ */
+FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c, int64_t M,
+                         int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
+                         void* workspace, size_t workspace_bytes, int* status_dev, feather_stream_t stream);
+
+/* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K).  Pass the same
+ * `variant` (or NULL) as to feather_scaled_mm_ex. */
+FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant);
+
+/* Writes the variant the library would choose for (M,N,K) on the current device into *out.
+ * Stands in for the autotuner of kernel/hip/utils.py:192-223 (`old_autotune`). */
+FEATHER_API int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t workspace_bytes, feather_mm_variant* out);
+
+/* ---------------------------------------------------------------------------------------------
+ * Weight format: quantise, prepack, inverse
+ * ------------------------------------------------------------------------------------------- */
+
+/* comfy_feather/quant.py:52-74 `quantize_fp8e5m2_scaled` followed by quant.py:11-13 `prepack_transpose`.
+ *   src        [N,K] row-major, dtype per src_dtype (fp32 / bf16 / fp16), K % 16 == 0
+ *   premul     fp32[1] or NULL: loader path `weight.float() * scale` (quant.py:128) applied to fp32 input
+ *              before the amax (only valid with FEATHER_SRC_FP32)
+ *   scale_io   fp32[1]: if recalc_scale != 0 it receives amax|x|/57344 (0 -> 1, fp16 clamp of quant.py:56-58);
+ *              otherwise it is read as the given scale
+ *   amax_scratch  uint32[2] scratch, any contents
+ *   dst        [K/16, N, 16] e5m2 bytes
+ * Round-to-nearest-even only (the seed = None / 0 branch, quant.py:72-73). */
+FEATHER_API int feather_quantize_prepack(const void* src, int src_dtype, const float* premul, int64_t N, int64_t K, int recalc_scale,
+                             float* scale_io, uint32_t* amax_scratch, uint8_t* dst, feather_stream_t stream);
+
+/* quant.py:11-13 `prepack_transpose` on bytes: [N,K] -> [K/16,N,16]  (e5m2 checkpoints, quant.py:125-126);
+ * also kernel/hip/hip_kernel.py:170-171 `prepack_b_for_scaled_mm` when src_is_kn != 0 (src is [K,N]). */
+FEATHER_API int feather_prepack_bytes(const uint8_t* src, int64_t N, int64_t K, int src_is_kn, uint8_t* dst, feather_stream_t stream);
+
+/* quant.py:17-19 `unprepack_transpose`: [K/16,N,16] -> [N,K] bytes (state_dict_tensors, quant.py:108-113). */
+FEATHER_API int feather_unprepack_bytes(const uint8_t* src, int64_t N, int64_t K, uint8_t* dst, feather_stream_t stream);
+
+/* quant.py:98-102 `FeatherFP8E5M2PackedLayout.dequantize`: unprepack -> fp32 * scale -> dst dtype
+ * (FEATHER_SRC_* codes), dst [N,K] row-major. */
+FEATHER_API int feather_dequantize(const uint8_t* src_prepacked, const float* scale, int64_t N, int64_t K, int dst_dtype, void* dst,
+                       feather_stream_t stream);
+
+/* kernel/convert.py:24-34 `bf16_to_fp16` (elementwise, round-to-nearest-even like `x.to(torch.float16)`). */
+FEATHER_API int feather_bf16_to_fp16(const uint16_t* src, uint16_t* dst, int64_t n, feather_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Library state
+ * ------------------------------------------------------------------------------------------- */
+FEATHER_API const char* feather_last_error_string(void);
+/* Library version as major*10000 + minor*100 + patch. */
+FEATHER_API int feather_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FEATHER_B200_H_ */
