@@ -98,7 +98,8 @@ FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, 
                          void* workspace, size_t workspace_bytes, int* status_dev, feather_stream_t stream);
 
 /* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K).  Pass the same
- * `variant` (or NULL) as to feather_scaled_mm_ex. */
+ * `variant` (or NULL) as to feather_scaled_mm_ex.  The reference's shipped kernel never splits K (README.md:31
+ * names an unshipped split-k branch), so its launcher has no scratch argument (kernel/hip/hip_kernel.cu:564-582). */
 FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant);
 
 /* Writes the variant the library would choose for (M,N,K) on the current device into *out.

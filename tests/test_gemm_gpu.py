@@ -1,0 +1,245 @@
+"""GPU parity tests of the mixed-precision GEMM, through the operator surface and the C ABI.
+
+Checker: the numpy oracle (fp32-product math of kernel/naive.py) and the fixtures made by the reference's own
+kernel/naive.py.  Tolerances: north-star gate max|err| <= 1e-2 * rms(out) (one-ulp rounding-boundary flips set aside
+for bf16, see tests/util.py), plus the reference's own gate (fro <= 0.01, max_abs <= 2 fp16 / 16 bf16,
+test_scaled_mm_hip.py:26-30) against verbatim naive.py output.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import feather_oracle as fo
+from tests.golden import cases
+from tests.util import TORCH_DT, assert_gemm_close, from_torch, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(native, dev, a, bq, scale, bias, out_dtype, variant=None):
+    A = to_torch(a, "fp16", dev)
+    B = to_torch(bq, "e5m2", dev)
+    S = torch.tensor([float(scale)], dtype=torch.float32, device=dev) if scale is not None else None
+    Bi = to_torch(bias, out_dtype, dev) if bias is not None else None
+    C = torch.full((a.shape[0], bq.shape[1]), float("nan"), dtype=TORCH_DT[out_dtype], device=dev)
+    native.scaled_mm_into(A, B, S, Bi, C, variant=native.make_variant(*variant) if variant else None)
+    native.check_device_status(dev)
+    return from_torch(C)
+
+
+def _synthetic(M, N, K, out_dtype, seed, bias=True):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+    w = (rng.standard_normal((N, K), dtype=np.float32) / np.float32(np.sqrt(K))).astype(np.float32)
+    bq, s = fo.make_feather_quantized_weight(w, "fp32", None)
+    b = fo.from_f32(rng.standard_normal((N,), dtype=np.float32), out_dtype) if bias else None
+    return a, bq, s, b
+
+
+@pytest.mark.parametrize("name", list(cases.GEMM_REF_CASES))
+def test_reference_distribution_through_operator(golden, hip_kernel, native, cuda_dev, name):
+    """The reference's own test recipe (test_scaled_mm_hip.py:9-32): prepack_b_for_scaled_mm + scaled_mm_hip_configured
+    against scaled_mm_naive, on its distribution, with its tolerances; here naive's output is the stored fixture."""
+    c = cases.gemm_ref_case(name)
+    a = to_torch(c["a"], "fp16", cuda_dev)
+    b_kn = to_torch(c["b_kn"], "e5m2", cuda_dev)
+    scale = torch.tensor(float(c["scale"]), dtype=torch.float32, device=cuda_dev)
+    bias = to_torch(c["bias"], c["out_dtype"], cuda_dev)
+    b_pp = hip_kernel.prepack_b_for_scaled_mm(b_kn)
+    assert np.array_equal(from_torch(b_pp), c["b_prepacked"])
+    for cfg in (hip_kernel._CONFIGS[0], hip_kernel._CONFIGS[-1], (1, 8, 4, 8, 2)):
+        out = hip_kernel.scaled_mm_hip_configured(a, b_pp, scale, bias, TORCH_DT[c["out_dtype"]], *cfg)
+        native.check_device_status(cuda_dev)
+        got = from_torch(out)
+        rep = fo.error_report(got, golden[f"gemm/{name}/out"], c["out_dtype"])
+        assert rep["fro_rel"] <= 0.01 and rep["max_abs"] <= (2.0 if c["out_dtype"] == "fp16" else 16.0), rep
+        ref32 = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp32")
+        assert_gemm_close(got, ref32, c["out_dtype"], fo, name)
+
+
+@pytest.mark.parametrize("name", list(cases.GEMM_BENCH_CASES))
+def test_benchmark_distribution(golden, hip_kernel, native, cuda_dev, name):
+    c = cases.gemm_bench_case(name)
+    out = hip_kernel.scaled_mm_hip(
+        to_torch(c["a"], "fp16", cuda_dev),
+        to_torch(c["b_prepacked"], "e5m2", cuda_dev),
+        torch.tensor(float(c["scale"]), dtype=torch.float32, device=cuda_dev),
+        to_torch(c["bias"], c["out_dtype"], cuda_dev) if c["bias"] is not None else None,
+        TORCH_DT[c["out_dtype"]],
+    )
+    native.check_device_status(cuda_dev)
+    got = from_torch(out)
+    rows = golden[f"gemm/{name}/rows"]
+    assert_gemm_close(got[rows], golden[f"gemm/{name}/out_rows"], c["out_dtype"], fo, name + " vs fixture")
+    ref = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp32")
+    assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle")
+
+
+# (M, N, K, out_dtype, (tokens_tile, cta_pair, split_k, transform_groups, max_ctas), bias, scale)
+VARIANT_CASES = [
+    (16, 128, 64, "fp16", (16, 1, 1, 2, 0), False, True),
+    (16, 128, 128, "fp16", (16, 1, 1, 1, 0), True, True),
+    (128, 128, 512, "fp16", (128, 1, 1, 2, 0), True, True),
+    (256, 128, 512, "bf16", (256, 1, 1, 2, 0), True, True),
+    (100, 72, 80, "bf16", (128, 1, 1, 2, 0), True, True),          # ragged in every dimension
+    (1, 256, 512, "bf16", (16, 1, 1, 2, 0), False, True),           # a single token
+    (33, 200, 48, "fp16", (64, 1, 1, 2, 0), True, True),            # K = 48: last k-block three quarters empty
+    (33, 200, 48, "fp16", (32, 1, 1, 2, 0), True, False),           # no scale
+    (7, 8, 16, "fp16", (16, 1, 1, 2, 0), True, True),               # smallest legal K, tiny N
+    (700, 640, 2048, "bf16", (256, 1, 1, 2, 0), True, True),
+    (700, 640, 2048, "fp16", (128, 1, 1, 2, 8), True, True),        # persistent: 8 CTAs walk 30 tiles
+    (520, 384, 1024, "fp16", (256, 1, 1, 1, 2), False, True),
+    (16, 256, 2048, "bf16", (16, 1, 4, 2, 0), True, True),          # split-K
+    (128, 384, 4096, "fp16", (128, 1, 8, 2, 0), True, True),
+    (40, 1000, 1040, "fp16", (64, 1, 3, 2, 5), True, True),         # split-K, uneven slices, few CTAs
+    (32, 256, 128, "fp16", (32, 2, 1, 2, 0), False, True),          # CTA pairs
+    (256, 256, 512, "fp16", (256, 2, 1, 2, 0), True, True),
+    (700, 640, 2048, "bf16", (256, 2, 1, 2, 0), True, True),
+    (700, 600, 2048, "fp16", (128, 2, 1, 1, 8), True, True),        # pairs, N not a multiple of 256
+    (64, 512, 4096, "fp16", (64, 2, 4, 2, 0), True, True),          # pairs + split-K
+    (16, 5120, 1024, "bf16", None, True, True),                     # library-chosen variant
+    (300, 1024, 1024, "bf16", None, False, True),
+]
+
+
+@pytest.mark.parametrize("M,N,K,out_dtype,variant,bias,scale", VARIANT_CASES)
+def test_variants_against_oracle(native, cuda_dev, M, N, K, out_dtype, variant, bias, scale):
+    a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 7 + N * 3 + K, bias=bias)
+    got = _run(native, cuda_dev, a, bq, s if scale else None, b, out_dtype, variant)
+    ref = fo.scaled_mm(a, bq, s if scale else None, b, out_dtype, product="fp32")
+    assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}")
+
+
+def test_split_k_workspace_is_reusable(native, cuda_dev):
+    """Back-to-back split-K launches on one workspace: the tile counters must be back at zero after each."""
+    a, bq, s, b = _synthetic(48, 384, 2048, "bf16", seed=3)
+    ref = fo.scaled_mm(a, bq, s, b, "bf16", product="fp32")
+    for _ in range(3):
+        got = _run(native, cuda_dev, a, bq, s, b, "bf16", (64, 1, 4, 2, 0))
+        assert_gemm_close(got, ref, "bf16", fo)
+    ws = native.workspace_for(cuda_dev)
+    assert int(ws[:4096].view(torch.int32).abs().sum().item()) == 0
+
+
+def test_tile_variants_agree_bitwise(native, cuda_dev):
+    """Without split-K every variant adds the k-blocks of an output element in the same order."""
+    a, bq, s, b = _synthetic(300, 512, 1536, "bf16", seed=9)
+    outs = [_run(native, cuda_dev, a, bq, s, b, "bf16", v) for v in ((256, 1, 1, 2, 0), (128, 1, 1, 1, 0), (64, 1, 1, 2, 0), (256, 2, 1, 2, 0))]
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+
+
+def test_empty_and_edge_shapes(hip_kernel, native, cuda_dev):
+    b = torch.zeros((4, 64, 16), dtype=torch.uint8, device=cuda_dev).view(torch.float8_e5m2)
+    a0 = torch.zeros((0, 64), dtype=torch.float16, device=cuda_dev)
+    out = hip_kernel.scaled_mm_hip(a0, b, None, None, torch.float16)
+    assert out.shape == (0, 64)
+    # zero activations: output is exactly the bias
+    a = torch.zeros((5, 64), dtype=torch.float16, device=cuda_dev)
+    bias = torch.randn(64, device=cuda_dev).to(torch.bfloat16)
+    w = torch.randint(0, 0x7B, (4, 64, 16), dtype=torch.uint8, device=cuda_dev).view(torch.float8_e5m2)
+    out = hip_kernel.scaled_mm_hip(a, w, torch.tensor(3.0, device=cuda_dev), bias, torch.bfloat16)
+    native.check_device_status(cuda_dev)
+    assert torch.equal(out, bias[None, :].expand(5, 64))
+
+
+def test_argument_checks(hip_kernel, cuda_dev):
+    """Same preconditions and messages as the reference op (hip_kernel.cu:648-730)."""
+    a = torch.zeros((16, 64), dtype=torch.float16, device=cuda_dev)
+    b = torch.zeros((4, 32, 16), dtype=torch.uint8, device=cuda_dev).view(torch.float8_e5m2)
+    c = torch.empty((16, 32), dtype=torch.float16, device=cuda_dev)
+    op = torch.ops.feather_ops.scaled_mm
+    cfg = (1, 8, 4, 8, 2)
+    with pytest.raises(RuntimeError, match="a must be float16"):
+        op(a.float(), b, None, None, c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="b_prepacked.shape\\[0\\] must equal K/16"):
+        op(a, b[:3], None, None, c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="scale must be float32"):
+        op(a, b, torch.ones(1, dtype=torch.float16, device=cuda_dev), None, c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="bias must have N elements"):
+        op(a, b, None, torch.zeros(31, dtype=torch.float16, device=cuda_dev), c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="bias must have the same dtype as c"):
+        op(a, b, None, torch.zeros(32, dtype=torch.bfloat16, device=cuda_dev), c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="c.shape\\[1\\] must equal N"):
+        op(a, b, None, None, c[:, :16], *cfg, 1)
+    with pytest.raises(RuntimeError, match="fp8e4m3"):
+        op(a, b.view(torch.uint8).view(torch.float8_e4m3fn), None, None, c, *cfg, 0)
+    with pytest.raises(RuntimeError, match="a.stride\\(1\\) must be 1"):
+        op(torch.zeros((64, 16), dtype=torch.float16, device=cuda_dev).t(), b, None, None, c, *cfg, 1)
+
+
+def test_reference_c_abi_signature(native, cuda_dev):
+    """`launch_scaled_mm` keeps the reference's argument order (hip_kernel.cu:564-582) and returns 1 / 0 like its bool."""
+    a, bq, s, b = _synthetic(64, 256, 512, "fp16", seed=5)
+    A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
+    S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+    Bi = to_torch(b, "fp16", cuda_dev)
+    C = torch.empty((64, 256), dtype=torch.float16, device=cuda_dev)
+    assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C) == 1
+    torch.cuda.synchronize()
+    assert_gemm_close(from_torch(C), fo.scaled_mm(a, bq, s, b, "fp16"), "fp16", fo)
+    assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C, b_dtype=0) == 0      # e4m3 is not supported
+
+
+def test_column_shard_writes_in_place(native, cuda_dev):
+    """Two weight shards along N write their column blocks of one [M,N] buffer; the result is bitwise the unsharded one."""
+    a, bq, s, b = _synthetic(200, 512, 1024, "bf16", seed=8)
+    full = _run(native, cuda_dev, a, bq, s, b, "bf16")
+    A = to_torch(a, "fp16", cuda_dev)
+    S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+    C = torch.zeros((200, 512), dtype=torch.bfloat16, device=cuda_dev)
+    for r in range(2):
+        Bs = to_torch(np.ascontiguousarray(bq[:, r * 256:(r + 1) * 256, :]), "e5m2", cuda_dev)
+        bias_s = to_torch(b[r * 256:(r + 1) * 256], "bf16", cuda_dev)
+        native.scaled_mm_into(A, Bs, S, bias_s, C[:, r * 256:(r + 1) * 256])
+    native.check_device_status(cuda_dev)
+    assert np.array_equal(from_torch(C), full)
+
+
+@pytest.mark.parametrize("K,N", [(5120, 13824), (13824, 5120), (5120, 5120)])
+def test_full_size_wan_shapes_properties(native, cuda_dev, K, N):
+    """M = 32768 Wan-14B linears.  The CPU oracle cannot do 4.6 TFLOP in seconds, so: rows sampled across the whole
+    output against the oracle, and exact properties that hold at any size (scaling A by 2 doubles the output bit for bit;
+    permuting token rows permutes output rows)."""
+    M = 32768
+    g = torch.Generator(device=cuda_dev).manual_seed(K + N)
+    A = torch.randn((M, K), generator=g, device=cuda_dev, dtype=torch.float32).to(torch.float16)
+    w = torch.randn((N, K), generator=g, device=cuda_dev, dtype=torch.float32) / K ** 0.5
+    B, S = native.quantize_prepack(w)
+    del w
+    S = S.reshape(1)
+    C = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_dev)
+    native.scaled_mm_into(A, B, S, None, C)
+    native.check_device_status(cuda_dev)
+    rows = np.unique(np.concatenate([np.arange(0, M, 4099), [M - 1, 255, 256, M - 257]]))
+    ref = fo.scaled_mm(from_torch(A[rows]), from_torch(B), np.float32(S.item()), None, "bf16", product="fp32")
+    assert_gemm_close(from_torch(C[rows]), ref, "bf16", fo, "sampled rows")
+    # linearity in powers of two is exact (no overflow at this scale)
+    C2 = torch.empty_like(C)
+    native.scaled_mm_into(A * 2, B, S, None, C2)
+    assert torch.equal(C2.view(torch.int16), (C.float() * 2).to(torch.bfloat16).view(torch.int16))
+    # row permutation
+    perm = torch.randperm(M, generator=g, device=cuda_dev)
+    native.scaled_mm_into(A[perm].contiguous(), B, S, None, C2)
+    native.check_device_status(cuda_dev)
+    assert torch.equal(C2.view(torch.int16), C[perm].view(torch.int16))
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("K,N", [(5120, 13824), (13824, 5120)])
+def test_small_m_sweep(native, cuda_dev, M, K, N):
+    """The bandwidth-bound sweep of the benchmark, full K and N, checked in full against the oracle."""
+    a, bq, s, _ = _synthetic(M, N, K, "bf16", seed=M + K, bias=False)
+    got = _run(native, cuda_dev, a, bq, s, None, "bf16")
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"M={M}")
+
+
+@pytest.mark.parametrize("K,N", [(3072, 3072), (3072, 9216), (3072, 12288), (12288, 3072)])
+def test_qwen_image_shapes(native, cuda_dev, K, N):
+    """M = 4352 (4096 image + 256 text tokens), fp16 out; 64 sampled rows against the oracle."""
+    M = 4352
+    a, bq, s, _ = _synthetic(M, N, K, "fp16", seed=K + N, bias=False)
+    got = _run(native, cuda_dev, a, bq, s, None, "fp16")
+    rows = np.arange(0, M, 68)
+    assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}")
