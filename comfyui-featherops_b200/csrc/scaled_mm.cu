@@ -5,7 +5,7 @@
 //
 //   out^T tile [128 weight columns n  x  TN tokens]  +=  up(W)[128 n x 16 k]  *  A^T[16 k x TN tokens]
 //
-//   producer warp   TMA: W bytes  [4 k16-blocks][128 n][16 B] (the prepacked layout, verbatim)  -> smem ring
+//   producer warp   TMA: W bytes  [4 k16-blocks][128 n][16 B] (the prepacked layout, verbatim; 2 KB rows) -> smem ring
 //                   TMA: A tokens [TN rows][64 k] fp16, 128-byte swizzle                         -> smem ring
 //   transform warps ld.shared 16 B (one n, 16 k) -> 8 x prmt (e5m2 -> fp16 is `byte << 8`, exact)
 //                   -> tcgen05.st into a TMEM ring (32 columns per 64-k stage); fp16 W never touches smem
@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -39,10 +40,13 @@ constexpr int kBW = 128;                      // weight columns per CTA = MMA M 
 constexpr int kBK = 64;                       // k per pipeline stage
 constexpr int kKSteps = kBK / 16;             // MMA k-steps per stage
 constexpr int kWStageBytes = kBW * kBK;       // e5m2 bytes per stage
-constexpr int kTStages = 4;                   // TMEM ring depth for upcast weights
+constexpr int kMaxTStages = 8;                // TMEM ring depth for upcast weights (upper bound)
 constexpr int kTColsPerStage = kBK / 2;       // 32-bit TMEM columns per stage (two fp16 per column)
 constexpr int kEpilogueWarps = 4;
 constexpr int kMaxStages = 24;
+// Split-K workspace: a fixed-size block of tile counters first (so the counters of any launch only ever overlap the counters of
+// another, which every launch leaves at zero), then the fp32 partial tiles.
+constexpr size_t kCounterBytes = 65536;
 
 __host__ __device__ constexpr int pow2_at_least(int x) {
     int p = 32;
@@ -52,22 +56,27 @@ __host__ __device__ constexpr int pow2_at_least(int x) {
 
 template <int TN, int CG>
 struct Cfg {
-    static_assert(TN == 16 || TN == 32 || TN == 64 || TN == 128 || TN == 256, "tokens tile");
+    static_assert(TN == 16 || TN == 32 || TN == 64 || TN == 128 || TN == 192 || TN == 256, "tokens tile");
     static_assert(CG == 1 || CG == 2, "cta group");
     static constexpr int kTokLoad = TN / CG;              // token rows this CTA loads per stage
     static constexpr int kAStageBytes = kTokLoad * 128;   // 64 fp16 per row
     static constexpr int kStageBytes = kWStageBytes + kAStageBytes;
-    static constexpr int kAccs = (TN <= 128) ? 2 : 1;     // accumulator buffers in TMEM
+    static constexpr int kAccs = (TN <= 192) ? 2 : 1;     // accumulator buffers in TMEM (two: the epilogue overlaps the next tile)
     static constexpr int kAccCols = kAccs * TN;
+    static constexpr int kTStagesRaw = (512 - kAccCols) / kTColsPerStage;
+    static constexpr int kTStages = kTStagesRaw > kMaxTStages ? kMaxTStages : kTStagesRaw;   // TMEM ring depth
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kTStages * kTColsPerStage);
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes;
+    static constexpr int kOutRows = TN < 32 ? TN : 32;                   // token rows per output staging buffer
+    static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [rows][128 n] 16-bit
+    static constexpr int kOutBytes = 2 * kOutBufBytes;                   // double buffered
+    static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
     static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > kMaxStages ? kMaxStages : kStagesRaw;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kBarrierBytes + 1024;
     static_assert(kTmemCols <= 512, "TMEM columns");
     static_assert(kAStageBytes % 1024 == 0, "swizzle atom alignment of token stages");
-    static_assert((3 * kMaxStages + 2 * kTStages + 2 * 2 + 1) * 8 + 16 <= kBarrierBytes, "barrier block");
+    static_assert((3 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8 + 16 <= kBarrierBytes, "barrier block");
 };
 
 struct MmParams {
@@ -77,9 +86,14 @@ struct MmParams {
     float* ws_partials;
     int* ws_counters;
     int* status;
+    long long* stats;   // optional [32] cycle counters written by CTA 0 (profiling aid), or null
     int M, N, K;
     long long ldc;
     int out_bf16;
+    int debug;     // FEATHER_DEBUG_FLAGS, timing experiments only (results are wrong): 1 = epilogue skips stores, 2 = also skips
+                   // TMEM loads, 16 = transform warps skip the upcast work; with 1 set: 32 = no proxy fence, 64 = no named barriers,
+                   // 128 = no staging writes.  None of them changes the mbarrier protocol.
+    int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
     int splits;
     int tiles_n, tiles_t, num_units, total_kb;
 };
@@ -93,8 +107,15 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
     Unit w;
     w.tile = u / p.splits;
     w.split = u - w.tile * p.splits;
-    const int nt = w.tile % p.tiles_n;
-    const int tt = w.tile / p.tiles_n;
+    // Tiles are walked in bands of kBand token tiles, token tile fastest inside a band, so the CTAs that run at the same time
+    // share a few token tiles and a few weight tiles (L2 locality) instead of one token tile and every weight tile.
+    constexpr int kBand = 8;
+    const int band_tiles = kBand * p.tiles_n;
+    const int band = w.tile / band_tiles;
+    const int in_band = w.tile - band * band_tiles;
+    const int rows = p.tiles_t - band * kBand < kBand ? p.tiles_t - band * kBand : kBand;
+    const int nt = in_band / rows;
+    const int tt = band * kBand + in_band % rows;
     w.n0 = nt * kBW * CG;
     w.tok0 = tt * TN;
     const int base = p.total_kb / p.splits;
@@ -103,6 +124,22 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
     w.kb_count = base + (w.split < rem ? 1 : 0);
     return w;
 }
+
+// Optional cycle accounting (MmParams::stats): each role of CTA 0 sums the SM cycles it spends in each of its waits.
+// slots: 0 producer total, 1 producer wait stage-free | 4 mma total, 5 mma wait acc-free, 6 mma wait tokens, 7 mma wait weights
+//        8 transform(warp 0 of group 0) total, 9 wait weight bytes, 10 wait tmem-free | 12 epilogue(warp 0) total, 13 wait acc-full,
+//        14 inside store chunks, 15 chunks
+struct StatTimer {
+    long long t0;
+    bool on;
+    __device__ __forceinline__ explicit StatTimer(bool enabled) : t0(0), on(enabled) {}
+    __device__ __forceinline__ void start() {
+        if (on) t0 = clock64();
+    }
+    __device__ __forceinline__ void stop(long long& acc) {
+        if (on) acc += clock64() - t0;
+    }
+};
 
 // role ids recorded in the status word: bits 8..15
 enum { kRoleProducer = 1, kRoleMma = 2, kRoleTransform = 3, kRoleEpilogue = 4 };
@@ -129,11 +166,27 @@ __device__ __forceinline__ uint16_t finish_value(float acc, float scale, bool ou
     return __half_as_ushort(v);
 }
 
+// Two accumulator values of one output column (tokens j and j+1) -> packed out-dtype pair {lo = token j, hi = token j+1}:
+// fp32 multiply by the scale, one packed round-to-nearest-even conversion, then the bias add in the output dtype.
+__device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float scale, bool out_bf16, bool has_bias, uint32_t bias2) {
+    const float r0 = acc0 * scale, r1 = acc1 * scale;
+    if (out_bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(r0, r1);
+        if (has_bias) v = __hadd2(v, *reinterpret_cast<const __nv_bfloat162*>(&bias2));
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(r0, r1);
+    if (has_bias) v = __hadd2(v, *reinterpret_cast<const __half2*>(&bias2));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 template <int TN, int CG, int TG>
 __global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2), 1)
-scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const MmParams p) {
+scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_c, const MmParams p) {
     using C = Cfg<TN, CG>;
     constexpr int kStages = C::kStages;
+    constexpr int kTStages = C::kTStages;
     constexpr int kAccs = C::kAccs;
     constexpr int kFirstTransformWarp = kEpilogueWarps;
     constexpr int kProducerWarp = kEpilogueWarps + 4 * TG;
@@ -146,18 +199,19 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     const uint32_t smem_a = smem_base;                                   // [kStages][kAStageBytes]
     const uint32_t smem_w = smem_base + kStages * C::kAStageBytes;       // [kStages][kWStageBytes]
-    const uint32_t bar_base = smem_base + kStages * C::kStageBytes;      // barrier block
-    uint8_t* const bar_gen = smem_gen + kStages * C::kStageBytes;
+    const uint32_t smem_out = smem_base + kStages * C::kStageBytes;      // [2][kOutRows][128] 16-bit output staging
+    const uint32_t bar_base = smem_out + C::kOutBytes;                   // barrier block
+    uint8_t* const bar_gen = smem_gen + kStages * C::kStageBytes + C::kOutBytes;
 
     const uint32_t bar_wfull = bar_base;                                 // [kStages]
     const uint32_t bar_afull = bar_wfull + 8 * kMaxStages;               // [kStages]
     const uint32_t bar_sempty = bar_afull + 8 * kMaxStages;              // [kStages]
     const uint32_t bar_tfull = bar_sempty + 8 * kMaxStages;              // [kTStages]
-    const uint32_t bar_tempty = bar_tfull + 8 * kTStages;                // [kTStages]
-    const uint32_t bar_accfull = bar_tempty + 8 * kTStages;              // [2]
+    const uint32_t bar_tempty = bar_tfull + 8 * kMaxTStages;             // [kTStages]
+    const uint32_t bar_accfull = bar_tempty + 8 * kMaxTStages;           // [2]
     const uint32_t bar_accempty = bar_accfull + 8 * 2;                   // [2]
     const uint32_t bar_drain = bar_accempty + 8 * 2;                     // [1]
-    constexpr int kWordsOff = (3 * kMaxStages + 2 * kTStages + 2 * 2 + 1) * 8;
+    constexpr int kWordsOff = (3 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8;
     volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + kWordsOff);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(bar_gen + kWordsOff + 4);
     volatile int* const last_flag = reinterpret_cast<volatile int*>(bar_gen + kWordsOff + 8);
@@ -191,6 +245,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     if (warp == kProducerWarp && lane == 0) {
         prefetch_tmap(&tmap_w);
         prefetch_tmap(&tmap_a);
+        if (p.tma_store) prefetch_tmap(&tmap_c);
     }
     if (warp == kMmaWarp) {
         tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -212,19 +267,26 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const bool stat = p.stats != nullptr && blockIdx.x == 0;
+            StatTimer tt(stat), tw(stat);
+            long long st_total = 0, st_wait = 0;
+            tt.start();
             for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
                 const Unit w = decode_unit<TN, CG>(p, u);
                 for (int i = 0; i < w.kb_count; ++i, ++it) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!mbar_wait<kPair>(bar_sempty + 8 * s, ph ^ 1u, abort_flag)) {
+                    tw.start();
+                    const bool free_ok = mbar_wait(bar_sempty + 8 * s, ph ^ 1u, abort_flag);
+                    tw.stop(st_wait);
+                    if (!free_ok) {
                         give_up<CG>(p, abort_flag, kRoleProducer, s);
                         ok = false;
                         break;
                     }
                     const int kb = w.kb_begin + i;
                     mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
-                    tma_load_3d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, 0, w.n0 + static_cast<int>(rank) * kBW,
+                    tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, (w.n0 + static_cast<int>(rank) * kBW) * 2,
                                 kb * kKSteps);
                     if constexpr (!kPair) {
                         mbar_arrive_expect_tx(bar_afull + 8 * s, C::kAStageBytes);
@@ -236,6 +298,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                          w.tok0 + static_cast<int>(rank) * C::kTokLoad);
                     }
                 }
+            }
+            tt.stop(st_total);
+            if (stat) {
+                p.stats[0] = st_total;
+                p.stats[1] = st_wait;
             }
             if (!ok) {
                 // Let this CTA's own copies land before shared memory goes away: bounded wait on the
@@ -258,11 +325,20 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             constexpr uint32_t idesc = umma_idesc_f16(kBW * CG, TN);
             uint32_t it = 0, ui = 0;
             bool ok = true;
+            const bool stat = p.stats != nullptr && blockIdx.x == 0;
+            StatTimer tt(stat), tw(stat);
+            long long st_total = 0, st_acc = 0, st_tok = 0, st_wgt = 0;
+            long long st_issue = 0;
+            long long st_tok_head = 0, st_wgt_head = 0, st_tok_events = 0, st_wgt_events = 0, st_tok_max = 0, st_wgt_max = 0;
+            tt.start();
             for (int u = cluster_id; ok && u < p.num_units; u += num_clusters, ++ui) {
                 const Unit w = decode_unit<TN, CG>(p, u);
                 const uint32_t a = ui % kAccs;
                 const uint32_t aph = (ui / kAccs) & 1u;
-                if (!mbar_wait<kPair>(bar_accempty + 8 * a, aph ^ 1u, abort_flag)) {
+                tw.start();
+                const bool acc_ok = mbar_wait(bar_accempty + 8 * a, aph ^ 1u, abort_flag);
+                tw.stop(st_acc);
+                if (!acc_ok) {
                     give_up<CG>(p, abort_flag, kRoleMma, 0x100);
                     break;
                 }
@@ -273,17 +349,37 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint32_t ph = (it / kStages) & 1u;
                     const uint32_t t = it % kTStages;
                     const uint32_t tph = (it / kTStages) & 1u;
-                    if (!mbar_wait<kPair>(bar_afull + 8 * s, ph, abort_flag)) {
+                    tw.start();
+                    const bool tok_ok = mbar_wait(bar_afull + 8 * s, ph, abort_flag);
+                    tw.stop(st_tok);
+                    if (stat) {
+                        const long long dt = clock64() - tw.t0;
+                        if (i < kStages) st_tok_head += dt;
+                        if (dt > 200) ++st_tok_events;
+                        if (dt > st_tok_max) st_tok_max = dt;
+                    }
+                    if (!tok_ok) {
                         give_up<CG>(p, abort_flag, kRoleMma, 0x200 | s);
                         ok = false;
                         break;
                     }
-                    if (!mbar_wait<kPair>(bar_tfull + 8 * t, tph, abort_flag)) {
+                    tw.start();
+                    const bool wgt_ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag);
+                    tw.stop(st_wgt);
+                    if (stat) {
+                        const long long dt = clock64() - tw.t0;
+                        if (i < kStages) st_wgt_head += dt;
+                        if (dt > 200) ++st_wgt_events;
+                        if (dt > st_wgt_max) st_wgt_max = dt;
+                    }
+                    if (!wgt_ok) {
                         give_up<CG>(p, abort_flag, kRoleMma, 0x300 | t);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    long long t_issue = 0;
+                    if (stat) t_issue = clock64();
                     const uint32_t a_tmem = tmem_wring + t * kTColsPerStage;
                     const uint64_t b_desc = umma_desc_kmajor_sw128(smem_a + s * C::kAStageBytes);
 #pragma unroll
@@ -298,12 +394,28 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         umma_commit_pair(bar_sempty + 8 * s, 0x3);
                         umma_commit_pair(bar_tempty + 8 * t, 0x3);
                     }
+                    if (stat) st_issue += clock64() - t_issue;
                 }
                 if (!ok) break;
                 if constexpr (!kPair)
                     umma_commit_1cta(bar_accfull + 8 * a);
                 else
                     umma_commit_pair(bar_accfull + 8 * a, 0x3);
+            }
+            tt.stop(st_total);
+            if (stat) {
+                p.stats[4] = st_total;
+                p.stats[5] = st_acc;
+                p.stats[6] = st_tok;
+                p.stats[7] = st_wgt;
+                p.stats[16] = st_tok_head;      // token waits during the first kStages k-blocks of a tile
+                p.stats[17] = st_wgt_head;
+                p.stats[18] = st_tok_events;    // waits longer than 200 cycles
+                p.stats[19] = st_wgt_events;
+                p.stats[20] = st_tok_max;
+                p.stats[21] = st_wgt_max;
+                p.stats[22] = it;               // k-blocks issued
+                p.stats[23] = st_issue;         // cycles between the waits and the end of the commits (4 MMAs + 2 commits)
             }
             // Nothing of this CTA pair may be torn down while an MMA is still reading it.
             umma_commit_1cta(bar_drain);
@@ -321,6 +433,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
+        const bool stat = p.stats != nullptr && blockIdx.x == 0 && warp == kFirstTransformWarp;
+        StatTimer tt(stat), tw(stat);
+        long long st_total = 0, st_bytes = 0, st_tmem = 0;
+        tt.start();
         for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
             const Unit w = decode_unit<TN, CG>(p, u);
             for (int i = 0; i < w.kb_count; ++i, ++it) {
@@ -329,9 +445,13 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const uint32_t ph = (it / kStages) & 1u;
                 const uint32_t t = it % kTStages;
                 const uint32_t tph = (it / kTStages) & 1u;
-                bool got = mbar_wait<false>(bar_wfull + 8 * s, ph, abort_flag);
-                got = got && mbar_wait<kPair>(bar_tempty + 8 * t, tph ^ 1u, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) {
+                tw.start();
+                bool got = mbar_wait_warp(bar_wfull + 8 * s, ph, abort_flag, lane);
+                tw.stop(st_bytes);
+                tw.start();
+                got = got && mbar_wait_warp(bar_tempty + 8 * t, tph ^ 1u, abort_flag, lane);
+                tw.stop(st_tmem);
+                if (!got) {
                     if (lane == 0) give_up<CG>(p, abort_flag, kRoleTransform, (q << 8) | s);
                     ok = false;
                     break;
@@ -339,23 +459,24 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t src = smem_w + s * kWStageBytes + w_lane_off;
                 const uint32_t dst = tmem_wring + t_lane + t * kTColsPerStage;
+                if ((p.debug & 16) == 0) {
+                    uint32_t x[kKSteps][4];
 #pragma unroll
-                for (int j = 0; j < kKSteps; ++j) {
-                    uint32_t x0, x1, x2, x3;
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3)
-                                 : "r"(src + j * (kBW * 16)));
-                    uint32_t v[8];
-                    // bytes b0..b3 of a word are k, k+1, k+2, k+3; fp16(b) = b << 8
-                    v[0] = __byte_perm(x0, 0u, 0x1404);
-                    v[1] = __byte_perm(x0, 0u, 0x3424);
-                    v[2] = __byte_perm(x1, 0u, 0x1404);
-                    v[3] = __byte_perm(x1, 0u, 0x3424);
-                    v[4] = __byte_perm(x2, 0u, 0x1404);
-                    v[5] = __byte_perm(x2, 0u, 0x3424);
-                    v[6] = __byte_perm(x3, 0u, 0x1404);
-                    v[7] = __byte_perm(x3, 0u, 0x3424);
-                    tmem_st_32x32b_x8(dst + j * 8, v);
+                    for (int j = 0; j < kKSteps; ++j)
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(x[j][0]), "=r"(x[j][1]), "=r"(x[j][2]), "=r"(x[j][3])
+                                     : "r"(src + j * (kBW * 16)));
+#pragma unroll
+                    for (int j = 0; j < kKSteps; ++j) {
+                        uint32_t v[8];
+                        // bytes b0..b3 of a word are k, k+1, k+2, k+3; fp16(b) = b << 8
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[2 * i] = __byte_perm(x[j][i], 0u, 0x1404);
+                            v[2 * i + 1] = __byte_perm(x[j][i], 0u, 0x3424);
+                        }
+                        tmem_st_32x32b_x8(dst + j * 8, v);
+                    }
                 }
                 tc_wait_st();
                 tc_fence_before();
@@ -369,6 +490,12 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
             }
         }
+        tt.stop(st_total);
+        if (stat && lane == 0) {
+            p.stats[8] = st_total;
+            p.stats[9] = st_bytes;
+            p.stats[10] = st_tmem;
+        }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 0..3)
         const int q = warp;
@@ -378,62 +505,136 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const bool has_bias = p.bias != nullptr;
         uint16_t* const c16 = reinterpret_cast<uint16_t*>(p.c);
         constexpr int kTileCols = kBW * CG;
+        constexpr int kOutRows = C::kOutRows;
+        const bool staged = p.tma_store != 0 && p.splits == 1;
         uint32_t ui = 0;
-        // A warp whose wait ran out stays in the loop as a bystander (alive = false): it touches no
-        // tensor memory but still joins the named barriers of the split-K path, so the other
-        // epilogue warps can never be left waiting for it.
+        uint32_t chunk_no = 0;     // output chunks issued so far: picks the staging buffer
+        // A warp whose wait ran out stays in the loop as a bystander (alive = false): it touches no tensor
+        // memory but still joins every named barrier, so the other epilogue warps are never left waiting.
         bool alive = true;
+        const bool stat = p.stats != nullptr && blockIdx.x == 0 && warp == 0;
+        StatTimer tt(stat), tw(stat);
+        long long st_total = 0, st_full = 0, st_emit = 0, st_chunks = 0;
+        tt.start();
         for (int u = cluster_id; u < p.num_units; u += num_clusters, ++ui) {
-            if (!alive && p.splits == 1) break;
             const Unit w = decode_unit<TN, CG>(p, u);
             const uint32_t a = ui % kAccs;
             const uint32_t aph = (ui / kAccs) & 1u;
             if (alive) {
-                const bool got = mbar_wait<kPair>(bar_accfull + 8 * a, aph, abort_flag);
-                if (!__all_sync(0xffffffffu, got)) {
+                tw.start();
+                const bool got = mbar_wait_warp(bar_accfull + 8 * a, aph, abort_flag, lane);
+                tw.stop(st_full);
+                if (!got) {
                     if (lane == 0) give_up<CG>(p, abort_flag, kRoleEpilogue, q);
                     alive = false;
-                    if (p.splits == 1) break;
                 }
             }
             tc_fence_after();
-            const int col = static_cast<int>(rank) * kBW + q * 32 + lane;  // column inside the tile
+            const int col_local = q * 32 + lane;                                  // column inside this CTA's 128
+            const int col = static_cast<int>(rank) * kBW + col_local;             // column inside the tile
             const int n = w.n0 + col;
             const bool n_ok = n < p.N;
             const uint16_t bias_bits = (has_bias && n_ok) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + n) : uint16_t(0);
             const uint32_t src = tmem_base + t_lane + a * TN;
+            const int valid = p.M - w.tok0 < TN ? p.M - w.tok0 : TN;              // token columns of this tile that exist
+            const bool skip_loads = !alive || (p.debug & 2) != 0;
+
             if (p.splits == 1) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < TN; c0 += 16) {
-                    if (w.tok0 + c0 >= p.M) break;
-                    uint32_t v[16];
-                    tmem_ld_32x32b_x16(src + c0, v);
-                    tc_wait_ld();
-                    if (n_ok) {
+                uint16_t* const c_col = c16 + static_cast<long long>(w.tok0) * p.ldc + n;
+                const bool direct_store = !staged && n_ok && alive && (p.debug & 1) == 0;
+                const bool dry = (p.debug & 1) != 0;                              // timing experiments: no store is issued
+                const bool odd = (lane & 1) != 0;
+                const uint32_t pick = odd ? 0x3276u : 0x5410u;
+                const uint32_t bias2 = static_cast<uint32_t>(bias_bits) * 0x00010001u;
+                const uint32_t lane_off = (col_local & ~1) * 2 + (odd ? kBW * 2 : 0);
+
+                // 16 accumulator columns (token rows c0 .. c0+15 of this tile) held in registers -> output.
+                // Staged path: lanes 2i and 2i+1 hold neighbouring output columns; each converts token pairs of its own
+                // column into packed words, swaps them with its neighbour and picks, with one byte permute, the 32-bit word
+                // {column 2i, column 2i+1} of one token row (even lane: the pair's first token, odd lane: the second).
+                // Sub-word shared-memory stores, and one fused convert-exchange-store loop, were both several times slower.
+                auto emit16 = [&](const uint32_t (&v)[16], int c0, uint32_t buf_rows) {
+                    if (staged) {
+                        uint32_t h[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            h[j] = finish_pair(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), scale, out_bf16, has_bias, bias2);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) h[j] = __byte_perm(h[j], __shfl_xor_sync(0xffffffffu, h[j], 1), pick);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) asm volatile("st.shared.u32 [%0], %1;" ::"r"(buf_rows + lane_off + 2 * j * (kBW * 2)), "r"(h[j]));
+                    } else if (direct_store) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const int tok = w.tok0 + c0 + j;
-                            if (tok < p.M)
-                                c16[static_cast<long long>(tok) * p.ldc + n] =
-                                    finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits);
+                            if (c0 + j < valid)
+                                c_col[static_cast<long long>(c0 + j) * p.ldc] = finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits);
                         }
                     }
+                };
+                // chunk = kOutRows token rows = one staging buffer = one TMA store
+                auto chunk_begin = [&]() -> uint32_t {
+                    const uint32_t buf = smem_out + (chunk_no & 1u) * C::kOutBufBytes;
+                    if (staged) {
+                        if (threadIdx.x == 0) tma_store_wait_read<1>();           // the store that last read this buffer is done with it
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                    }
+                    return buf;
+                };
+                auto chunk_end = [&](uint32_t buf, int c0) {
+                    if (staged) {
+                        fence_proxy_async_smem();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (threadIdx.x == 0 && !dry) {
+                            tma_store_2d(&tmap_c, buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
+                            tma_store_commit();
+                        }
+                        ++chunk_no;
+                    }
+                    ++st_chunks;
+                };
+                tw.start();
+                uint32_t va[16] = {}, vb[16] = {};
+                if (!skip_loads) tmem_ld_32x32b_x16(src, va);
+                if constexpr (TN == 16) {
+                    if (!skip_loads) tc_wait_ld();
+                    const uint32_t buf = chunk_begin();
+                    emit16(va, 0, buf);
+                    chunk_end(buf, 0);
+                } else {
+                    // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
+#pragma unroll 1
+                    for (int c0 = 0; c0 < valid; c0 += 32) {
+                        if (!skip_loads) {
+                            tc_wait_ld();
+                            tmem_ld_32x32b_x16(src + c0 + 16, vb);
+                        }
+                        const uint32_t buf = chunk_begin();
+                        emit16(va, c0, buf);
+                        if (!skip_loads) {
+                            tc_wait_ld();
+                            if (c0 + 32 < valid) tmem_ld_32x32b_x16(src + c0 + 32, va);
+                        }
+                        emit16(vb, c0 + 16, buf + 16 * kBW * 2);
+                        chunk_end(buf, c0);
+                    }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    if constexpr (!kPair)
-                        mbar_arrive(bar_accempty + 8 * a);
-                    else
-                        mbar_arrive_cluster(mapa_u32(bar_accempty + 8 * a, 0));
+                tw.stop(st_emit);
+                if (alive) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (!kPair)
+                            mbar_arrive(bar_accempty + 8 * a);
+                        else
+                            mbar_arrive_cluster(mapa_u32(bar_accempty + 8 * a, 0));
+                    }
                 }
             } else {
                 // split-K: park this slice's fp32 partial, then the last slice to arrive reduces in slice order
                 float* const part = p.ws_partials + (static_cast<long long>(w.tile) * p.splits + w.split) * (TN * kTileCols);
                 if (alive) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < TN; c0 += 16) {
-                        if (w.tok0 + c0 >= p.M) break;
+                    for (int c0 = 0; c0 < valid; c0 += 16) {
                         uint32_t v[16];
                         tmem_ld_32x32b_x16(src + c0, v);
                         tc_wait_ld();
@@ -463,13 +664,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const float* const tile_part = p.ws_partials + static_cast<long long>(w.tile) * p.splits * (TN * kTileCols);
                     if (n_ok && alive) {
 #pragma unroll 1
-                        for (int c = 0; c < TN; ++c) {
-                            const int tok = w.tok0 + c;
-                            if (tok >= p.M) break;
+                        for (int c = 0; c < valid; ++c) {
                             float acc = 0.0f;
                             for (int sp = 0; sp < p.splits; ++sp)
                                 acc += __ldcg(tile_part + static_cast<long long>(sp) * (TN * kTileCols) + c * kTileCols + col);
-                            c16[static_cast<long long>(tok) * p.ldc + n] = finish_value(acc, scale, out_bf16, has_bias, bias_bits);
+                            c16[static_cast<long long>(w.tok0 + c) * p.ldc + n] = finish_value(acc, scale, out_bf16, has_bias, bias_bits);
                         }
                     }
                 }
@@ -477,6 +676,14 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (is_last && threadIdx.x == 0) *counter = 0;    // ready for the next launch
             }
         }
+        tt.stop(st_total);
+        if (stat && lane == 0) {
+            p.stats[12] = st_total;
+            p.stats[13] = st_full;
+            p.stats[14] = st_emit;
+            p.stats[15] = st_chunks;
+        }
+        if (threadIdx.x == 0) tma_store_wait_all<0>();           // shared memory must outlive the stores that read it
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -535,7 +742,7 @@ struct Plan {
     size_t ws_bytes, counter_bytes;
 };
 
-static bool valid_tn(int tn) { return tn == 16 || tn == 32 || tn == 64 || tn == 128 || tn == 256; }
+static bool valid_tn(int tn) { return tn == 16 || tn == 32 || tn == 64 || tn == 128 || tn == 192 || tn == 256; }
 
 // Shape heuristic.  Stands in for the reference's per-shape autotune over 28 tile configs
 // (kernel/hip/utils.py:192-223): here the tile is fixed by the token count and the machine is filled by
@@ -571,7 +778,8 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
             if (splits < 1) splits = 1;
         }
         const size_t per_split = static_cast<size_t>(tiles) * tn * kBW * cg * sizeof(float);
-        const size_t counters = ((static_cast<size_t>(tiles) * cg * sizeof(int) + 255) / 256) * 256;
+        const size_t counters = kCounterBytes;
+        if (static_cast<size_t>(tiles) * cg * sizeof(int) > kCounterBytes) splits = 1;
         if (ws_known && splits > 1 && counters + per_split * splits > ws_avail) {
             // shrink to what the caller's scratch can hold
             size_t fit = ws_avail > counters ? (ws_avail - counters) / per_split : 0;
@@ -579,9 +787,10 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
         }
     }
     if (splits < 1 || splits > pl.total_kb) return false;
+    if (splits > 1 && static_cast<size_t>(tiles) * cg * sizeof(int) > kCounterBytes) return false;
     pl.splits = splits;
     pl.num_units = static_cast<int>(tiles) * splits;
-    pl.counter_bytes = splits > 1 ? ((static_cast<size_t>(tiles) * cg * sizeof(int) + 255) / 256) * 256 : 0;
+    pl.counter_bytes = splits > 1 ? kCounterBytes : 0;
     pl.ws_bytes = splits > 1 ? pl.counter_bytes + static_cast<size_t>(tiles) * splits * tn * kBW * cg * sizeof(float) : 0;
     pl.max_ctas = v ? v->max_ctas : 0;
     *out = pl;
@@ -589,7 +798,8 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
 }
 
 template <int TN, int CG, int TG>
-static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const MmParams& p, int grid, cudaStream_t stream) {
+static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const CUtensorMap& tc, const MmParams& p, int grid,
+                                  cudaStream_t stream) {
     using C = Cfg<TN, CG>;
     auto kernel = scaled_mm_kernel<TN, CG, TG>;
     static std::mutex mu;
@@ -617,14 +827,15 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tw, ta, p);
+    return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, p);
 }
 
 template <int TN>
-static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const MmParams& p, int grid, cudaStream_t s) {
-    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, p, grid, s);
+static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const CUtensorMap& tc, const MmParams& p, int grid,
+                             cudaStream_t s) {
+    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
     if constexpr (TN >= 32)
-        return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, p, grid, s);
+        return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
     return cudaErrorInvalidValue;
 }
 
@@ -659,14 +870,19 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return set_error(FEATHER_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
 
-    CUtensorMap tmap_w, tmap_a;
+    CUtensorMap tmap_w, tmap_a, tmap_c;
+    memset(&tmap_c, 0, sizeof(tmap_c));
+    // TMA stores need 16-byte aligned output rows; otherwise (odd ldc, split-K) the epilogue stores 2 bytes at a time
+    const bool tma_store = pl.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0;
     {
-        // W bytes as a rank-3 tensor (16, N, K/16); a box is 4 k16-blocks x 128 n x 16 B, laid down verbatim.
-        const cuuint64_t dims[3] = {16, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(K / 16)};
-        const cuuint64_t strides[2] = {16, static_cast<cuuint64_t>(N) * 16};
-        const cuuint32_t box[3] = {16, kBW, kKSteps};
-        const cuuint32_t estr[3] = {1, 1, 1};
-        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(b), dims, strides, box, estr,
+        // W as 8-byte elements: one k16-block plane is a row of 2N elements (n-major, 16 B per n), so the 128 n of a tile
+        // are 2048 contiguous bytes = 256 elements.  A box is 4 planes x 256 elements and lands as [4][128 n][16 B].
+        // (A byte-typed box with a 16-byte inner extent would make the copy engine issue 512 16-byte rows per stage.)
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N) * 2, static_cast<cuuint64_t>(K / 16)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 16};
+        const cuuint32_t box[2] = {kBW * 2, kKSteps};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(b), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
@@ -683,7 +899,19 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with CUresult %d", static_cast<int>(r));
     }
 
+    if (tma_store) {
+        // C as (N, M) 16-bit with row pitch ldc; a box is 128 n x (up to 32) token rows, clipped at N and M
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * 2};
+        const cuuint32_t box[2] = {kBW, static_cast<cuuint32_t>(pl.tn < 32 ? pl.tn : 32)};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = encode(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
+    }
+
     MmParams p{};
+    p.tma_store = tma_store ? 1 : 0;
     p.scale = scale;
     p.bias = bias;
     p.c = c;
@@ -695,6 +923,9 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.K = static_cast<int>(K);
     p.ldc = ldc;
     p.out_bf16 = output_dtype == FEATHER_OUT_BF16 ? 1 : 0;
+    if (const char* dbg = getenv("FEATHER_DEBUG_FLAGS")) p.debug = atoi(dbg);
+    // FEATHER_STATS=1: the caller's status buffer is at least 8 + 32*8 bytes and receives the cycle counters of CTA 0 after the status word
+    if (status_dev != nullptr && getenv("FEATHER_STATS") != nullptr) p.stats = reinterpret_cast<long long*>(status_dev + 2);
     p.splits = pl.splits;
     p.tiles_n = pl.tiles_n;
     p.tiles_t = pl.tiles_t;
@@ -709,11 +940,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
 
     cudaError_t e = cudaErrorInvalidValue;
     switch (pl.tn) {
-        case 16: e = launch_tn<16>(pl.cg, tg, tmap_w, tmap_a, p, grid, stream); break;
-        case 32: e = launch_tn<32>(pl.cg, tg, tmap_w, tmap_a, p, grid, stream); break;
-        case 64: e = launch_tn<64>(pl.cg, tg, tmap_w, tmap_a, p, grid, stream); break;
-        case 128: e = launch_tn<128>(pl.cg, tg, tmap_w, tmap_a, p, grid, stream); break;
-        case 256: e = launch_tn<256>(pl.cg, tg, tmap_w, tmap_a, p, grid, stream); break;
+        case 16: e = launch_tn<16>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 32: e = launch_tn<32>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 64: e = launch_tn<64>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 128: e = launch_tn<128>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 192: e = launch_tn<192>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 256: e = launch_tn<256>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
         default: break;
     }
     if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "scaled_mm launch failed: %s", cudaGetErrorString(e));

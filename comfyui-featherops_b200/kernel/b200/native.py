@@ -162,7 +162,8 @@ def status_word_for(device):
     with _scratch_lock:
         st = _status_words.get(key)
         if st is None:
-            st = torch.zeros(1, dtype=torch.int32, device=device)
+            # word 0: status; words 2.. : 32 int64 cycle counters filled when FEATHER_STATS is set (profiling aid)
+            st = torch.zeros(2 + 64, dtype=torch.int32, device=device)
             _status_words[key] = st
         return st
 
@@ -185,7 +186,7 @@ def check_device_status(device=None):
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     st = status_word_for(device)
-    value = int(st.item())
+    value = int(st[0].item())
     if value != 0:
         st.zero_()
         role = (value >> 8) & 0xFF
@@ -195,6 +196,19 @@ def check_device_status(device=None):
             f"scaled_mm kernel reported status {value & 0xFF} ({names.get(role, 'role ' + str(role))}, detail 0x{detail:x}): "
             "a bounded wait ran out and the kernel returned early; the output is not valid"
         )
+
+
+def read_stats(device):
+    """Cycle counters of CTA 0 from the last scaled_mm launch made with FEATHER_STATS=1 in the environment."""
+    torch.cuda.synchronize(device)
+    v = status_word_for(device)[2:66].view(torch.int64).cpu().tolist()
+    return {
+        "producer": {"total": v[0], "wait_stage_free": v[1]},
+        "mma": {"total": v[4], "wait_acc_free": v[5], "wait_tokens": v[6], "wait_weights": v[7]},
+        "mma_detail": {"tok_head": v[16], "wgt_head": v[17], "tok_events": v[18], "wgt_events": v[19], "tok_max": v[20], "wgt_max": v[21], "kblocks": v[22], "issue": v[23]},
+        "transform": {"total": v[8], "wait_weight_bytes": v[9], "wait_tmem_free": v[10]},
+        "epilogue": {"total": v[12], "wait_acc_full": v[13], "store_chunks": v[14], "chunks": v[15]},
+    }
 
 
 # ------------------------------------------------------------------------------------------------

@@ -57,6 +57,6 @@ class ColumnShardedLinear:
         if self.world == 1:
             return local
         m = a.shape[0]
-        gathered = torch.empty((self.world, m, self.n_local), dtype=out_dtype, device=a.device)
+        gathered = torch.empty((self.world * m, self.n_local), dtype=out_dtype, device=a.device)    # rank-major concatenation
         dist.all_gather_into_tensor(gathered, local, group=self.group)
-        return gathered.permute(1, 0, 2).reshape(m, self.n_total)
+        return gathered.view(self.world, m, self.n_local).permute(1, 0, 2).reshape(m, self.n_total)

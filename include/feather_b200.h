@@ -53,7 +53,7 @@ enum { FEATHER_OUT_FP16 = 0, FEATHER_OUT_BF16 = 1 };
 enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
 
 /* Kernel variant selection for feather_scaled_mm_ex.  All fields 0 = let the library choose.
- *   tokens_tile : activation rows per MMA tile (the MMA N extent): 16, 32, 64, 128 or 256
+ *   tokens_tile : activation rows per MMA tile (the MMA N extent): 16, 32, 64, 128, 192 or 256
  *   cta_pair    : 1 = one CTA per tile (128 weight columns), 2 = two-CTA pairs (256 weight columns)
  *   split_k     : number of K slices reduced through the fp32 workspace (1 = none)
  *   transform_groups : groups of four warps that upcast e5m2 weight stages (1 or 2)
@@ -88,7 +88,7 @@ FEATHER_API int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, cons
  *   c            out-dtype [M, ldc] row-major; only columns [0,N) of each row are written.  ldc >= N
  *                lets a column shard write straight into its slice of a wider output.
  *   workspace    scratch for split-K variants (may be NULL), 16-byte aligned.  It must be zero-filled
- *                once after allocation (tile counters live at its start); every launch that completes
+ *                once after allocation (tile counters live in its first 64 KiB); every launch that completes
  *                leaves the counters at zero again, so the same buffer serves any later call.
  *                Two launches that may overlap on the device need separate workspaces.
  *   status_dev   int32 device word or NULL; left untouched on success

@@ -239,7 +239,8 @@ def error_report(out, ref, out_dtype):
     r = to_f32(ref, out_dtype).astype(np.float64)
     finite = np.isfinite(r) & np.isfinite(o)
     same_nonfinite = np.array_equal(np.isnan(r), np.isnan(o)) and np.array_equal(np.isinf(r) * np.sign(r), np.isinf(o) * np.sign(o))
-    d = np.where(finite, o - r, 0.0)
+    with np.errstate(invalid="ignore"):
+        d = np.where(finite, o - r, 0.0)
     rms = float(np.sqrt(np.mean(np.where(finite, r, 0.0) ** 2)))
     fro = float(np.linalg.norm(d) / max(np.linalg.norm(np.where(finite, r, 0.0)), 1e-6))
     ob = np.asarray(out).view(np.uint16)

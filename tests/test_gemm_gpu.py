@@ -96,6 +96,10 @@ VARIANT_CASES = [
     (32, 256, 128, "fp16", (32, 2, 1, 2, 0), False, True),          # CTA pairs
     (256, 256, 512, "fp16", (256, 2, 1, 2, 0), True, True),
     (700, 640, 2048, "bf16", (256, 2, 1, 2, 0), True, True),
+    (700, 640, 2048, "bf16", (192, 2, 1, 2, 0), True, True),        # 192-token tiles: two accumulators in TMEM
+    (1000, 384, 1024, "fp16", (192, 1, 1, 2, 3), True, True),
+    (300, 520, 512, "bf16", (128, 1, 1, 2, 0), True, True),          # N % 8 == 0 but not a multiple of the tile
+    (90, 250, 256, "fp16", (128, 1, 1, 2, 0), True, True),           # N % 8 != 0: rows not 16-byte aligned, plain-store epilogue
     (700, 600, 2048, "fp16", (128, 2, 1, 1, 8), True, True),        # pairs, N not a multiple of 256
     (64, 512, 4096, "fp16", (64, 2, 4, 2, 0), True, True),          # pairs + split-K
     (16, 5120, 1024, "bf16", None, True, True),                     # library-chosen variant
@@ -118,8 +122,19 @@ def test_split_k_workspace_is_reusable(native, cuda_dev):
     for _ in range(3):
         got = _run(native, cuda_dev, a, bq, s, b, "bf16", (64, 1, 4, 2, 0))
         assert_gemm_close(got, ref, "bf16", fo)
+    # the tile counters occupy the first 64 KiB of the workspace
     ws = native.workspace_for(cuda_dev)
-    assert int(ws[:4096].view(torch.int32).abs().sum().item()) == 0
+    assert int(ws[:65536].view(torch.int32).abs().sum().item()) == 0
+
+
+def test_split_k_launches_of_different_tile_counts_share_a_workspace(native, cuda_dev):
+    """A launch with few tiles followed by one with many: the second one's counters must not see the first one's partials."""
+    a, bq, s, b = _synthetic(16, 256, 2048, "bf16", seed=31)
+    got = _run(native, cuda_dev, a, bq, s, b, "bf16", (16, 1, 4, 2, 0))
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
+    a, bq, s, b = _synthetic(16, 13824, 1024, "bf16", seed=32)
+    got = _run(native, cuda_dev, a, bq, s, b, "bf16", (16, 1, 4, 2, 0))
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
 
 
 def test_tile_variants_agree_bitwise(native, cuda_dev):
@@ -165,7 +180,7 @@ def test_argument_checks(hip_kernel, cuda_dev):
         op(a, b, None, None, c[:, :16], *cfg, 1)
     with pytest.raises(RuntimeError, match="fp8e4m3"):
         op(a, b.view(torch.uint8).view(torch.float8_e4m3fn), None, None, c, *cfg, 0)
-    with pytest.raises(RuntimeError, match="a.stride\\(1\\) must be 1"):
+    with pytest.raises(RuntimeError, match="a.stride\\(0\\) must equal K"):
         op(torch.zeros((64, 16), dtype=torch.float16, device=cuda_dev).t(), b, None, None, c, *cfg, 1)
 
 

@@ -1,0 +1,141 @@
+"""CPU: host-side logic that needs no GPU - the loader node, the sampling pin, LoRA patch arithmetic, weight sharding and the
+world-size-2 exchange of the column-sharded linear over gloo (the local GEMM is replaced by the CPU oracle port there)."""
+
+import importlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_loader_node_builds_ops_per_model_type(pkg):
+    loader = importlib.import_module("feather_b200.comfy_feather.loader")
+    import comfy.sd
+
+    node = loader.FeatherUNetLoader()
+    types = loader.FeatherUNetLoader.INPUT_TYPES()["required"]
+    assert types["model_type"][0] == ["default", "anima", "flux2", "qwen", "wan"]
+    (model,) = node.load_unet("model_a.safetensors", "wan")
+    ops = comfy.sd._last_call["model_options"]["custom_operations"]
+    assert comfy.sd._last_call["unet_path"].endswith("diffusion_models/model_a.safetensors")
+    assert ops._out_dtype == torch.float16 and "patch_embedding" in ops._excluded_names and "head" in ops._excluded_names
+    assert model._feather_sampling_model_pin and len(model.wrappers) == 1
+    node.load_unet("model_b.safetensors", "qwen")
+    ops = comfy.sd._last_call["model_options"]["custom_operations"]
+    assert ops._out_dtype == torch.bfloat16 and "img_mod" in ops._excluded_names
+    node.load_unet("model_b.safetensors", "default")
+    assert comfy.sd._last_call["model_options"]["custom_operations"]._excluded_names == ()
+
+
+def test_sampling_pin_keeps_active_model(pkg):
+    sampling = importlib.import_module("feather_b200.comfy_feather.sampling")
+    import comfy.model_management as mm
+
+    calls = []
+    mm.free_memory = lambda memory_required, device, keep_loaded=None, *a, **k: calls.append(list(keep_loaded or []))
+    if hasattr(mm, sampling._STATE):
+        delattr(mm, sampling._STATE)
+
+    class Patcher:
+        def __init__(self):
+            self.wrappers = []
+
+        def add_wrapper_with_key(self, t, k, fn):
+            self.wrappers.append(fn)
+
+    class Loaded:
+        def __init__(self, model):
+            self.model = model
+
+    p = Patcher()
+    sampling.install_sampling_model_pin(p)
+    sampling.install_sampling_model_pin(p)          # idempotent
+    assert len(p.wrappers) == 1
+    loaded = Loaded(p)
+    mm.current_loaded_models = [loaded, Loaded(object())]
+
+    class Executor:
+        class_obj = type("S", (), {"model_patcher": p})()
+
+        def __call__(self, *a, **k):
+            mm.free_memory(1 << 30, "cuda")
+            return "sampled"
+
+    assert p.wrappers[0](Executor()) == "sampled"
+    assert calls[-1] == [loaded]
+    mm.free_memory(1 << 30, "cuda")
+    assert calls[-1] == []                           # nothing pinned outside sampling
+
+
+def test_lora_patch_arithmetic(pkg):
+    lora = importlib.import_module("feather_b200.comfy_feather.lora")
+    from oracle import feather_oracle as fo
+
+    class Adapter:
+        def __init__(self, b, a, alpha):
+            self.weights = (b, a, alpha)
+
+    class PatchFn:
+        key = "w"
+
+        def __init__(self, patches):
+            self.patches = {"w": patches}
+
+    x = torch.randn(6, 32)
+    a1, b1 = torch.randn(4, 32), torch.randn(16, 4)
+    a2, b2 = torch.randn(2, 32), torch.randn(16, 2)
+    y = torch.zeros(6, 16)
+    out = lora.apply_lora_patches(x, y, [PatchFn([(0.5, Adapter(b1, a1, 8.0), 2.0, None, None), (1.0, Adapter(b2, a2, None), 0.25, None, None)])])
+    ref = fo.lora_delta(x.numpy(), a1.numpy(), b1.numpy(), 0.5 * 2.0 * 8.0 / 4) + fo.lora_delta(x.numpy(), a2.numpy(), b2.numpy(), 0.25)
+    assert out is y and np.allclose(out.numpy(), ref, atol=1e-4)
+    assert lora.apply_lora_patches(x, y, []) is y
+
+
+def test_shard_columns(pkg):
+    sharded = importlib.import_module("feather_b200.kernel.b200.sharded")
+    b = torch.arange(4 * 24 * 16, dtype=torch.int32).reshape(4, 24, 16).to(torch.uint8)
+    bias = torch.arange(24, dtype=torch.float32)
+    parts = [sharded.shard_columns(b, bias, r, 4) for r in range(4)]
+    assert all(p[0].is_contiguous() and p[0].shape == (4, 6, 16) for p in parts)
+    assert torch.equal(torch.cat([p[0] for p in parts], dim=1), b)
+    assert torch.equal(torch.cat([p[1] for p in parts]), bias)
+    with pytest.raises(ValueError, match="not divisible"):
+        sharded.shard_columns(b, None, 0, 5)
+
+
+def _sharded_worker(rank, world, port, tmpdir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "fake_comfy"))
+    import torch.distributed as dist
+
+    import __graft_entry__
+    from oracle import naive_torch
+
+    __graft_entry__.load_package()
+    sharded = importlib.import_module("feather_b200.kernel.b200.sharded")
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    torch.manual_seed(0)
+    M, K, N = 24, 64, 96
+    a = torch.randn(M, K).to(torch.float16)
+    bq, s = naive_torch.quantize_prepack_cpu(torch.randn(N, K) / 8)
+    bias = torch.randn(N).to(torch.bfloat16)
+    lin = sharded.ColumnShardedLinear(bq, s.reshape(1), bias, rank, world, torch.device("cpu"))
+    # the GEMM itself is CUDA-only; on CPU ranks stand in for it with the oracle port so the exchange can be tested
+    lin.gemm_only = lambda x, dt, variant=None, out=None: naive_torch.scaled_mm_cpu(x, lin.b_local, lin.scale, lin.bias_local, dt)
+    out = lin(a, torch.bfloat16)
+    full = naive_torch.scaled_mm_cpu(a, bq, s, bias, torch.bfloat16)
+    ok = out.shape == (M, N) and torch.equal(out.view(torch.int16), full.view(torch.int16))
+    with open(os.path.join(tmpdir, f"ok{rank}"), "w") as f:
+        f.write("1" if ok else "0")
+    dist.destroy_process_group()
+
+
+def test_column_sharded_exchange_world2_gloo(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_sharded_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [open(tmp_path / f"ok{r}").read() for r in range(2)] == ["1", "1"]
