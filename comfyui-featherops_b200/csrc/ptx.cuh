@@ -76,21 +76,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase (a failing try_wait parks the thread for microseconds; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gave up; once set, every
 // other wait returns false at once so the whole CTA drains.  Time limit: kWaitLimitNs of wall clock.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-#ifndef FEATHER_POLL_SLEEP_NS
-#define FEATHER_POLL_SLEEP_NS 32
-#endif
-constexpr unsigned kPollSleepNs = FEATHER_POLL_SLEEP_NS;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // Fast path: try_wait itself blocks for a hardware-defined interval, so a short run of attempts covers every
+    // ordinary wait without touching the timer.  (A nanosleep back-off here costs hundreds of cycles per wake-up.)
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(kPollSleepNs);   // parked polls otherwise crowd the shared-memory pipe the working warps need
         if (((++spins) & 63u) == 0u) {
             if (*abort_flag != 0) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) return false;

@@ -5,10 +5,10 @@
 //
 //   out^T tile [128 weight columns n  x  TN tokens]  +=  up(W)[128 n x 16 k]  *  A^T[16 k x TN tokens]
 //
-//   producer warp   TMA: W bytes  [4 k16-blocks][128 n][16 B] (the prepacked layout, verbatim; 2 KB rows) -> smem ring
-//                   TMA: A tokens [TN rows][64 k] fp16, 128-byte swizzle                         -> smem ring
+//   producer warps  TMA: W bytes  [8 k16-blocks][128 n][16 B] (the prepacked layout, verbatim; 2 KB rows) -> smem ring
+//                   TMA: A tokens 2 x [TN rows][64 k] fp16, 128-byte swizzle                     -> smem ring
 //   transform warps ld.shared 16 B (one n, 16 k) -> 8 x prmt (e5m2 -> fp16 is `byte << 8`, exact)
-//                   -> tcgen05.st into a TMEM ring (32 columns per 64-k stage); fp16 W never touches smem
+//                   -> tcgen05.st into a TMEM ring (64 columns per 128-k stage); fp16 W never touches smem
 //   MMA warp        tcgen05.mma kind::f16, A from TMEM, B (tokens) from smem descriptor, D fp32 in TMEM
 //   epilogue warps  tcgen05.ld -> *scale -> RTNE to out dtype -> +bias in out dtype -> global stores
 //                   (lane = n, so a warp writes 32 consecutive n of one token row); split-K slices park
@@ -37,13 +37,15 @@
 namespace feather {
 
 constexpr int kBW = 128;                      // weight columns per CTA = MMA M per CTA = TMEM lanes
-constexpr int kBK = 64;                       // k per pipeline stage
+constexpr int kBK = 128;                      // k per pipeline stage (one barrier round: 8 MMAs amortise the waits and commits)
+constexpr int kSubK = 64;                     // k per 128-byte-swizzled token sub-tile (64 fp16 = one 128-byte row)
+constexpr int kSubTiles = kBK / kSubK;        // token sub-tiles per stage
 constexpr int kKSteps = kBK / 16;             // MMA k-steps per stage
 constexpr int kWStageBytes = kBW * kBK;       // e5m2 bytes per stage
 constexpr int kMaxTStages = 8;                // TMEM ring depth for upcast weights (upper bound)
 constexpr int kTColsPerStage = kBK / 2;       // 32-bit TMEM columns per stage (two fp16 per column)
-constexpr int kEpilogueWarps = 4;
-constexpr int kMaxStages = 24;
+constexpr int kEpilogueWarps = 8;              // two groups of four (one warp per TMEM lane quarter in each)
+constexpr int kMaxStages = 16;
 // Split-K workspace: a fixed-size block of tile counters first (so the counters of any launch only ever overlap the counters of
 // another, which every launch leaves at zero), then the fp32 partial tiles.
 constexpr size_t kCounterBytes = 65536;
@@ -59,8 +61,8 @@ struct Cfg {
     static_assert(TN == 16 || TN == 32 || TN == 64 || TN == 128 || TN == 192 || TN == 256, "tokens tile");
     static_assert(CG == 1 || CG == 2, "cta group");
     static constexpr int kTokLoad = TN / CG;              // token rows this CTA loads per stage
-    static constexpr int kAStageBytes = kTokLoad * 128;   // 64 fp16 per row
-    static constexpr int kStageBytes = kWStageBytes + kAStageBytes;
+    static constexpr int kASubBytes = kTokLoad * 128;     // one sub-tile: 64 fp16 per row
+    static constexpr int kAStageBytes = kASubBytes * kSubTiles;
     static constexpr int kAccs = (TN <= 192) ? 2 : 1;     // accumulator buffers in TMEM (two: the epilogue overlaps the next tile)
     static constexpr int kAccCols = kAccs * TN;
     static constexpr int kTStagesRaw = (512 - kAccCols) / kTColsPerStage;
@@ -71,12 +73,17 @@ struct Cfg {
     static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [rows][128 n] 16-bit
     static constexpr int kOutBytes = 2 * kOutBufBytes;                   // double buffered
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
-    static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
-    static constexpr int kStages = kStagesRaw > kMaxStages ? kMaxStages : kStagesRaw;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kBarrierBytes + 1024;
+    // Two independent rings: token tiles (freed when the MMAs that read them retire) and raw weight bytes (freed as soon as
+    // the transform warps have read them).  The weight ring is one stage deeper so weights arrive ahead of the upcast.
+    static constexpr int kAStagesRaw = (kSmemBudget - kWStageBytes) / (kAStageBytes + kWStageBytes);
+    static constexpr int kAStages = kAStagesRaw > 12 ? 12 : kAStagesRaw;
+    static constexpr int kWStagesRaw = (kSmemBudget - kAStages * kAStageBytes) / kWStageBytes;
+    static constexpr int kWStages = kWStagesRaw > kMaxStages ? kMaxStages : kWStagesRaw;
+    static constexpr int kSmemBytes = kAStages * kAStageBytes + kWStages * kWStageBytes + kOutBytes + kBarrierBytes + 1024;
+    static_assert(kAStages >= 2 && kWStages >= 2, "ring depth");
     static_assert(kTmemCols <= 512, "TMEM columns");
-    static_assert(kAStageBytes % 1024 == 0, "swizzle atom alignment of token stages");
-    static_assert((3 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8 + 16 <= kBarrierBytes, "barrier block");
+    static_assert(kASubBytes % 1024 == 0, "swizzle atom alignment of token sub-tiles");
+    static_assert((4 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8 + 16 <= kBarrierBytes, "barrier block");
 };
 
 struct MmParams {
@@ -126,7 +133,7 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
 }
 
 // Optional cycle accounting (MmParams::stats): each role of CTA 0 sums the SM cycles it spends in each of its waits.
-// slots: 0 producer total, 1 producer wait stage-free | 4 mma total, 5 mma wait acc-free, 6 mma wait tokens, 7 mma wait weights
+// slots: 0 token producer total, 1 its wait for a free stage, 2/3 the same for the weight producer | 4 mma total, 5 mma wait acc-free, 6 mma wait tokens, 7 mma wait weights
 //        8 transform(warp 0 of group 0) total, 9 wait weight bytes, 10 wait tmem-free | 12 epilogue(warp 0) total, 13 wait acc-full,
 //        14 inside store chunks, 15 chunks
 struct StatTimer {
@@ -181,37 +188,41 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
 }
 
 template <int TN, int CG, int TG>
-__global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2), 1)
+__global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 3), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_c, const MmParams p) {
     using C = Cfg<TN, CG>;
-    constexpr int kStages = C::kStages;
+    constexpr int kAStages = C::kAStages;
+    constexpr int kWStages = C::kWStages;
     constexpr int kTStages = C::kTStages;
     constexpr int kAccs = C::kAccs;
     constexpr int kFirstTransformWarp = kEpilogueWarps;
     constexpr int kProducerWarp = kEpilogueWarps + 4 * TG;
     constexpr int kMmaWarp = kProducerWarp + 1;
+    constexpr int kWProducerWarp = kProducerWarp + 2;
     constexpr bool kPair = (CG == 2);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const uint32_t smem_a = smem_base;                                   // [kStages][kAStageBytes]
-    const uint32_t smem_w = smem_base + kStages * C::kAStageBytes;       // [kStages][kWStageBytes]
-    const uint32_t smem_out = smem_base + kStages * C::kStageBytes;      // [2][kOutRows][128] 16-bit output staging
+    const uint32_t smem_a = smem_base;                                   // [kAStages][kAStageBytes]
+    const uint32_t smem_w = smem_base + kAStages * C::kAStageBytes;      // [kWStages][kWStageBytes]
+    constexpr int kRingBytes = kAStages * C::kAStageBytes + kWStages * kWStageBytes;
+    const uint32_t smem_out = smem_base + kRingBytes;                    // [2][kOutRows][128] 16-bit output staging
     const uint32_t bar_base = smem_out + C::kOutBytes;                   // barrier block
-    uint8_t* const bar_gen = smem_gen + kStages * C::kStageBytes + C::kOutBytes;
+    uint8_t* const bar_gen = smem_gen + kRingBytes + C::kOutBytes;
 
-    const uint32_t bar_wfull = bar_base;                                 // [kStages]
-    const uint32_t bar_afull = bar_wfull + 8 * kMaxStages;               // [kStages]
-    const uint32_t bar_sempty = bar_afull + 8 * kMaxStages;              // [kStages]
-    const uint32_t bar_tfull = bar_sempty + 8 * kMaxStages;              // [kTStages]
+    const uint32_t bar_wfull = bar_base;                                 // [kWStages] weight bytes landed
+    const uint32_t bar_wempty = bar_wfull + 8 * kMaxStages;              // [kWStages] weight bytes read by the 4 transform warps
+    const uint32_t bar_afull = bar_wempty + 8 * kMaxStages;              // [kAStages] token tile landed (both CTAs of a pair)
+    const uint32_t bar_aempty = bar_afull + 8 * kMaxStages;              // [kAStages] token tile no longer read by any MMA
+    const uint32_t bar_tfull = bar_aempty + 8 * kMaxStages;              // [kTStages]
     const uint32_t bar_tempty = bar_tfull + 8 * kMaxTStages;             // [kTStages]
     const uint32_t bar_accfull = bar_tempty + 8 * kMaxTStages;           // [2]
     const uint32_t bar_accempty = bar_accfull + 8 * 2;                   // [2]
     const uint32_t bar_drain = bar_accempty + 8 * 2;                     // [1]
-    constexpr int kWordsOff = (3 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8;
+    constexpr int kWordsOff = (4 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8;
     volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + kWordsOff);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(bar_gen + kWordsOff + 4);
     volatile int* const last_flag = reinterpret_cast<volatile int*>(bar_gen + kWordsOff + 8);
@@ -223,10 +234,13 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int num_clusters = gridDim.x / CG;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kWStages; ++s) {
             mbar_init(bar_wfull + 8 * s, 1);
+            mbar_init(bar_wempty + 8 * s, 4);
+        }
+        for (int s = 0; s < kAStages; ++s) {
             mbar_init(bar_afull + 8 * s, CG);
-            mbar_init(bar_sempty + 8 * s, 4 + 1);
+            mbar_init(bar_aempty + 8 * s, 1);
         }
         for (int t = 0; t < kTStages; ++t) {
             mbar_init(bar_tfull + 8 * t, 4 * CG);
@@ -243,10 +257,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         fence_proxy_async_smem();
     }
     if (warp == kProducerWarp && lane == 0) {
-        prefetch_tmap(&tmap_w);
         prefetch_tmap(&tmap_a);
         if (p.tma_store) prefetch_tmap(&tmap_c);
     }
+    if (warp == kWProducerWarp && lane == 0) prefetch_tmap(&tmap_w);
     if (warp == kMmaWarp) {
         tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish<CG>();
@@ -262,9 +276,12 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_wring = tmem_base + C::kAccCols;   // column offset of the upcast-weight ring
 
-    if (warp == kProducerWarp) {
-        // ------------------------------------------------------------------ TMA producer (one lane)
+    if (warp == kProducerWarp || warp == kWProducerWarp) {
+        // ------------------------------------------------------------------ TMA producers (one lane each): token tiles / weight bytes
         if (lane == 0) {
+            const bool weights = warp == kWProducerWarp;
+            const uint32_t n_stages = weights ? kWStages : kAStages;
+            const uint32_t bar_free = weights ? bar_wempty : bar_aempty;
             uint32_t it = 0;
             bool ok = true;
             const bool stat = p.stats != nullptr && blockIdx.x == 0;
@@ -274,44 +291,51 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
                 const Unit w = decode_unit<TN, CG>(p, u);
                 for (int i = 0; i < w.kb_count; ++i, ++it) {
-                    const uint32_t s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+                    const uint32_t s = it % n_stages;
+                    const uint32_t ph = (it / n_stages) & 1u;
                     tw.start();
-                    const bool free_ok = mbar_wait(bar_sempty + 8 * s, ph ^ 1u, abort_flag);
+                    const bool free_ok = mbar_wait(bar_free + 8 * s, ph ^ 1u, abort_flag);
                     tw.stop(st_wait);
                     if (!free_ok) {
-                        give_up<CG>(p, abort_flag, kRoleProducer, s);
+                        give_up<CG>(p, abort_flag, kRoleProducer, (weights ? 0x100 : 0) | s);
                         ok = false;
                         break;
                     }
                     const int kb = w.kb_begin + i;
-                    mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
-                    tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, (w.n0 + static_cast<int>(rank) * kBW) * 2,
-                                kb * kKSteps);
-                    if constexpr (!kPair) {
+                    if (weights) {
+                        mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
+                        tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, (w.n0 + static_cast<int>(rank) * kBW) * 2, kb * kKSteps);
+                    } else if constexpr (!kPair) {
                         mbar_arrive_expect_tx(bar_afull + 8 * s, C::kAStageBytes);
-                        tma_load_2d(smem_a + s * C::kAStageBytes, &tmap_a, bar_afull + 8 * s, kb * kBK, w.tok0);
+#pragma unroll
+                        for (int sub = 0; sub < kSubTiles; ++sub)
+                            tma_load_2d(smem_a + s * C::kAStageBytes + sub * C::kASubBytes, &tmap_a, bar_afull + 8 * s, kb * kBK + sub * kSubK,
+                                        w.tok0);
                     } else {
                         const uint32_t leader_bar = mapa_u32(bar_afull + 8 * s, 0);
                         mbar_arrive_expect_tx_cluster(leader_bar, C::kAStageBytes);
-                        tma_load_2d_pair(smem_a + s * C::kAStageBytes, &tmap_a, leader_bar, kb * kBK,
-                                         w.tok0 + static_cast<int>(rank) * C::kTokLoad);
+#pragma unroll
+                        for (int sub = 0; sub < kSubTiles; ++sub)
+                            tma_load_2d_pair(smem_a + s * C::kAStageBytes + sub * C::kASubBytes, &tmap_a, leader_bar, kb * kBK + sub * kSubK,
+                                             w.tok0 + static_cast<int>(rank) * C::kTokLoad);
                     }
                 }
             }
             tt.stop(st_total);
             if (stat) {
-                p.stats[0] = st_total;
-                p.stats[1] = st_wait;
+                p.stats[weights ? 2 : 0] = st_total;
+                p.stats[weights ? 3 : 1] = st_wait;
             }
             if (!ok) {
-                // Let this CTA's own copies land before shared memory goes away: bounded wait on the
-                // weight barriers armed most recently, then a short fixed pause for the token loads.
-                const uint32_t back = it < static_cast<uint32_t>(kStages) ? it : static_cast<uint32_t>(kStages);
-                for (uint32_t j = 1; j <= back; ++j) {
-                    const uint32_t jt = it - j;
-                    const uint64_t t0 = globaltimer_ns();
-                    while (!mbar_try_wait(bar_wfull + 8 * (jt % kStages), (jt / kStages) & 1u) && globaltimer_ns() - t0 < 1000000ull) {
+                // Let this CTA's own copies land before shared memory goes away: a bounded wait on the weight barriers armed
+                // most recently, and a short fixed pause for the token loads (their barrier may live in the pair's other CTA).
+                if (weights) {
+                    const uint32_t back = it < n_stages ? it : n_stages;
+                    for (uint32_t j = 1; j <= back; ++j) {
+                        const uint32_t jt = it - j;
+                        const uint64_t t0 = globaltimer_ns();
+                        while (!mbar_try_wait(bar_wfull + 8 * (jt % n_stages), (jt / n_stages) & 1u) && globaltimer_ns() - t0 < 1000000ull) {
+                        }
                     }
                 }
                 const uint64_t t1 = globaltimer_ns();
@@ -329,6 +353,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             StatTimer tt(stat), tw(stat);
             long long st_total = 0, st_acc = 0, st_tok = 0, st_wgt = 0;
             long long st_issue = 0;
+            bool peek_tok = false, peek_wgt = false;
             long long st_tok_head = 0, st_wgt_head = 0, st_tok_events = 0, st_wgt_events = 0, st_tok_max = 0, st_wgt_max = 0;
             tt.start();
             for (int u = cluster_id; ok && u < p.num_units; u += num_clusters, ++ui) {
@@ -345,53 +370,58 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * TN;
                 for (int i = 0; i < w.kb_count; ++i, ++it) {
-                    const uint32_t s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
+                    const uint32_t s = it % kAStages;
+                    const uint32_t ph = (it / kAStages) & 1u;
                     const uint32_t t = it % kTStages;
                     const uint32_t tph = (it / kTStages) & 1u;
-                    tw.start();
-                    const bool tok_ok = mbar_wait(bar_afull + 8 * s, ph, abort_flag);
-                    tw.stop(st_tok);
-                    if (stat) {
-                        const long long dt = clock64() - tw.t0;
-                        if (i < kStages) st_tok_head += dt;
-                        if (dt > 200) ++st_tok_events;
-                        if (dt > st_tok_max) st_tok_max = dt;
+                    // `peek_*` were probed (non-blocking) before the previous k-block's MMAs were issued, so the barrier
+                    // latency overlapped with that issue; only a phase that was still pending then is waited for here.
+                    if (!peek_tok) {
+                        tw.start();
+                        const bool tok_ok = mbar_wait(bar_afull + 8 * s, ph, abort_flag);
+                        tw.stop(st_tok);
+                        ++st_tok_events;
+                        if (!tok_ok) {
+                            give_up<CG>(p, abort_flag, kRoleMma, 0x200 | s);
+                            ok = false;
+                            break;
+                        }
                     }
-                    if (!tok_ok) {
-                        give_up<CG>(p, abort_flag, kRoleMma, 0x200 | s);
-                        ok = false;
-                        break;
+                    if (!peek_wgt) {
+                        tw.start();
+                        const bool wgt_ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag);
+                        tw.stop(st_wgt);
+                        ++st_wgt_events;
+                        if (!wgt_ok) {
+                            give_up<CG>(p, abort_flag, kRoleMma, 0x300 | t);
+                            ok = false;
+                            break;
+                        }
                     }
-                    tw.start();
-                    const bool wgt_ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag);
-                    tw.stop(st_wgt);
-                    if (stat) {
-                        const long long dt = clock64() - tw.t0;
-                        if (i < kStages) st_wgt_head += dt;
-                        if (dt > 200) ++st_wgt_events;
-                        if (dt > st_wgt_max) st_wgt_max = dt;
-                    }
-                    if (!wgt_ok) {
-                        give_up<CG>(p, abort_flag, kRoleMma, 0x300 | t);
-                        ok = false;
-                        break;
+                    {
+                        const uint32_t itn = it + 1;
+                        peek_tok = mbar_test_wait(bar_afull + 8 * (itn % kAStages), (itn / kAStages) & 1u);
+                        peek_wgt = mbar_test_wait(bar_tfull + 8 * (itn % kTStages), (itn / kTStages) & 1u);
                     }
                     tc_fence_after();
                     long long t_issue = 0;
                     if (stat) t_issue = clock64();
                     const uint32_t a_tmem = tmem_wring + t * kTColsPerStage;
-                    const uint64_t b_desc = umma_desc_kmajor_sw128(smem_a + s * C::kAStageBytes);
 #pragma unroll
-                    for (int ks = 0; ks < kKSteps; ++ks) {
-                        // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
-                        umma_f16_ts<CG>(d_tmem, a_tmem + ks * 8, b_desc + static_cast<uint64_t>(ks * 2), idesc, (i | ks) != 0 ? 1u : 0u);
+                    for (int sub = 0; sub < kSubTiles; ++sub) {
+                        const uint64_t b_desc = umma_desc_kmajor_sw128(smem_a + s * C::kAStageBytes + sub * C::kASubBytes);
+#pragma unroll
+                        for (int ks = 0; ks < kSubK / 16; ++ks) {
+                            // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
+                            umma_f16_ts<CG>(d_tmem, a_tmem + (sub * (kSubK / 16) + ks) * 8, b_desc + static_cast<uint64_t>(ks * 2), idesc,
+                                            (i | sub | ks) != 0 ? 1u : 0u);
+                        }
                     }
                     if constexpr (!kPair) {
-                        umma_commit_1cta(bar_sempty + 8 * s);
+                        umma_commit_1cta(bar_aempty + 8 * s);
                         umma_commit_1cta(bar_tempty + 8 * t);
                     } else {
-                        umma_commit_pair(bar_sempty + 8 * s, 0x3);
+                        umma_commit_pair(bar_aempty + 8 * s, 0x3);
                         umma_commit_pair(bar_tempty + 8 * t, 0x3);
                     }
                     if (stat) st_issue += clock64() - t_issue;
@@ -441,8 +471,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const Unit w = decode_unit<TN, CG>(p, u);
             for (int i = 0; i < w.kb_count; ++i, ++it) {
                 if (static_cast<int>(it % TG) != g) continue;
-                const uint32_t s = it % kStages;
-                const uint32_t ph = (it / kStages) & 1u;
+                const uint32_t s = it % kWStages;
+                const uint32_t ph = (it / kWStages) & 1u;
                 const uint32_t t = it % kTStages;
                 const uint32_t tph = (it / kTStages) & 1u;
                 tw.start();
@@ -482,7 +512,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(bar_sempty + 8 * s);
+                    mbar_arrive(bar_wempty + 8 * s);
                     if constexpr (!kPair)
                         mbar_arrive(bar_tfull + 8 * t);
                     else
@@ -497,8 +527,12 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             p.stats[10] = st_tmem;
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 0..3)
-        const int q = warp;
+        // ------------------------------------------------------------------ epilogue (warps 0..7)
+        // Warp e reads the TMEM lanes of quarter e % 4 (its 32 output columns n); the two groups e / 4 take alternate blocks
+        // of kOutRows accumulator columns (token rows), each group with its own staging buffer and named barrier.
+        const int q = warp & 3;
+        const int grp = warp >> 2;
+        const bool group_leader = (threadIdx.x & 127) == 0;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
         const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
         const bool out_bf16 = p.out_bf16 != 0;
@@ -507,8 +541,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         constexpr int kTileCols = kBW * CG;
         constexpr int kOutRows = C::kOutRows;
         const bool staged = p.tma_store != 0 && p.splits == 1;
+        const uint32_t out_buf = smem_out + grp * C::kOutBufBytes;
         uint32_t ui = 0;
-        uint32_t chunk_no = 0;     // output chunks issued so far: picks the staging buffer
         // A warp whose wait ran out stays in the loop as a bystander (alive = false): it touches no tensor
         // memory but still joins every named barrier, so the other epilogue warps are never left waiting.
         bool alive = true;
@@ -525,7 +559,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const bool got = mbar_wait_warp(bar_accfull + 8 * a, aph, abort_flag, lane);
                 tw.stop(st_full);
                 if (!got) {
-                    if (lane == 0) give_up<CG>(p, abort_flag, kRoleEpilogue, q);
+                    if (lane == 0) give_up<CG>(p, abort_flag, kRoleEpilogue, warp);
                     alive = false;
                 }
             }
@@ -538,6 +572,21 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t src = tmem_base + t_lane + a * TN;
             const int valid = p.M - w.tok0 < TN ? p.M - w.tok0 : TN;              // token columns of this tile that exist
             const bool skip_loads = !alive || (p.debug & 2) != 0;
+            // The accumulator goes back to the MMA warp as soon as this warp's last TMEM load of the tile has landed.
+            bool released = false;
+            auto release_acc = [&]() {
+                if (released) return;
+                released = true;
+                if (!alive) return;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (!kPair)
+                        mbar_arrive(bar_accempty + 8 * a);
+                    else
+                        mbar_arrive_cluster(mapa_u32(bar_accempty + 8 * a, 0));
+                }
+            };
 
             if (p.splits == 1) {
                 uint16_t* const c_col = c16 + static_cast<long long>(w.tok0) * p.ldc + n;
@@ -571,100 +620,94 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         }
                     }
                 };
-                // chunk = kOutRows token rows = one staging buffer = one TMA store
-                auto chunk_begin = [&]() -> uint32_t {
-                    const uint32_t buf = smem_out + (chunk_no & 1u) * C::kOutBufBytes;
+                // one block = kOutRows token rows = this group's staging buffer = one TMA store
+                auto block_begin = [&]() {
                     if (staged) {
-                        if (threadIdx.x == 0) tma_store_wait_read<1>();           // the store that last read this buffer is done with it
-                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (group_leader) tma_store_wait_read<0>();              // the previous store of this group has read the buffer
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                     }
-                    return buf;
                 };
-                auto chunk_end = [&](uint32_t buf, int c0) {
+                auto block_end = [&](int c0) {
                     if (staged) {
                         fence_proxy_async_smem();
-                        asm volatile("bar.sync 2, 128;" ::: "memory");
-                        if (threadIdx.x == 0 && !dry) {
-                            tma_store_2d(&tmap_c, buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                        if (group_leader && !dry) {
+                            tma_store_2d(&tmap_c, out_buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
                             tma_store_commit();
                         }
-                        ++chunk_no;
                     }
                     ++st_chunks;
                 };
                 tw.start();
+                const int first = grp * kOutRows;                                  // this group's blocks: first, first + 2*kOutRows, ...
                 uint32_t va[16] = {}, vb[16] = {};
-                if (!skip_loads) tmem_ld_32x32b_x16(src, va);
-                if constexpr (TN == 16) {
-                    if (!skip_loads) tc_wait_ld();
-                    const uint32_t buf = chunk_begin();
-                    emit16(va, 0, buf);
-                    chunk_end(buf, 0);
-                } else {
-                    // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
+                if (first < valid && !skip_loads) tmem_ld_32x32b_x16(src + first, va);
 #pragma unroll 1
-                    for (int c0 = 0; c0 < valid; c0 += 32) {
+                for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
+                    const int next = c0 + 2 * kOutRows;
+                    if constexpr (kOutRows == 16) {
+                        if (!skip_loads) tc_wait_ld();
+                        if (next < valid) {
+                            if (!skip_loads) tmem_ld_32x32b_x16(src + next, vb);   // vb doubles as the next block's buffer
+                        } else {
+                            release_acc();
+                        }
+                        block_begin();
+                        emit16(va, c0, out_buf);
+                        block_end(c0);
+                        if (next < valid) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) va[j] = vb[j];
+                        }
+                    } else {
+                        // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
                         if (!skip_loads) {
                             tc_wait_ld();
                             tmem_ld_32x32b_x16(src + c0 + 16, vb);
                         }
-                        const uint32_t buf = chunk_begin();
-                        emit16(va, c0, buf);
-                        if (!skip_loads) {
-                            tc_wait_ld();
-                            if (c0 + 32 < valid) tmem_ld_32x32b_x16(src + c0 + 32, va);
+                        block_begin();
+                        emit16(va, c0, out_buf);
+                        if (!skip_loads) tc_wait_ld();
+                        if (next < valid) {
+                            if (!skip_loads) tmem_ld_32x32b_x16(src + next, va);
+                        } else {
+                            release_acc();
                         }
-                        emit16(vb, c0 + 16, buf + 16 * kBW * 2);
-                        chunk_end(buf, c0);
+                        emit16(vb, c0 + 16, out_buf + 16 * kBW * 2);
+                        block_end(c0);
                     }
                 }
+                release_acc();                                                     // a group without any block in this tile
                 tw.stop(st_emit);
-                if (alive) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (!kPair)
-                            mbar_arrive(bar_accempty + 8 * a);
-                        else
-                            mbar_arrive_cluster(mapa_u32(bar_accempty + 8 * a, 0));
-                    }
-                }
             } else {
                 // split-K: park this slice's fp32 partial, then the last slice to arrive reduces in slice order
                 float* const part = p.ws_partials + (static_cast<long long>(w.tile) * p.splits + w.split) * (TN * kTileCols);
                 if (alive) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < valid; c0 += 16) {
+                    for (int c0 = grp * 16; c0 < valid; c0 += 32) {
                         uint32_t v[16];
                         tmem_ld_32x32b_x16(src + c0, v);
                         tc_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) __stcg(part + (c0 + j) * kTileCols + col, __uint_as_float(v[j]));
                     }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (!kPair)
-                            mbar_arrive(bar_accempty + 8 * a);
-                        else
-                            mbar_arrive_cluster(mapa_u32(bar_accempty + 8 * a, 0));
-                    }
                 }
+                release_acc();
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 int* const counter = p.ws_counters + w.tile * CG + static_cast<int>(rank);
                 if (threadIdx.x == 0) {
                     const int old = atomicAdd(counter, 1);
                     *last_flag = (old == p.splits - 1) ? 1 : 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
                 const bool is_last = *last_flag != 0;
                 if (is_last) {
                     __threadfence();
                     const float* const tile_part = p.ws_partials + static_cast<long long>(w.tile) * p.splits * (TN * kTileCols);
                     if (n_ok && alive) {
 #pragma unroll 1
-                        for (int c = 0; c < valid; ++c) {
+                        for (int c = grp; c < valid; c += 2) {
                             float acc = 0.0f;
                             for (int sp = 0; sp < p.splits; ++sp)
                                 acc += __ldcg(tile_part + static_cast<long long>(sp) * (TN * kTileCols) + c * kTileCols + col);
@@ -672,7 +715,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         }
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone has read last_flag / the partials
+                asm volatile("bar.sync 1, 256;" ::: "memory");   // everyone has read last_flag / the partials
                 if (is_last && threadIdx.x == 0) *counter = 0;    // ready for the next launch
             }
         }
@@ -683,7 +726,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             p.stats[14] = st_emit;
             p.stats[15] = st_chunks;
         }
-        if (threadIdx.x == 0) tma_store_wait_all<0>();           // shared memory must outlive the stores that read it
+        if (group_leader) tma_store_wait_all<0>();               // shared memory must outlive the stores that read it
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -754,7 +797,7 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (!valid_tn(tn)) return false;
     int cg = v ? v->cta_pair : 0;
-    if (cg == 0) cg = 1;
+    if (cg == 0) cg = (M > 128 && N >= 2 * kBW) ? 2 : 1;   // CTA pairs halve the token-tile traffic per SM; small M is bound by the weight stream
     if (cg != 1 && cg != 2) return false;
     if (cg == 2 && tn < 32) return false;   // each CTA of a pair loads tn/2 token rows, at least one 8-row swizzle group x2
     pl.tn = tn;
@@ -770,10 +813,10 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     int splits = v ? v->split_k : 0;
     if (splits == 0) {
         splits = 1;
-        if (tiles < clusters && pl.total_kb >= 16) {
-            // aim at >= 2 work units per cluster, keep at least 8 k-blocks (512 k) per slice
+        if (tiles < clusters && pl.total_kb >= 8) {
+            // aim at >= 2 work units per cluster, keep at least 4 stages (512 k) per slice
             int want = static_cast<int>((2LL * clusters + tiles - 1) / tiles);
-            int cap = pl.total_kb / 8;
+            int cap = pl.total_kb / 4;
             splits = want < cap ? want : cap;
             if (splits < 1) splits = 1;
         }
@@ -817,7 +860,7 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-    cfg.blockDim = dim3(32 * (kEpilogueWarps + 4 * TG + 2), 1, 1);
+    cfg.blockDim = dim3(32 * (kEpilogueWarps + 4 * TG + 3), 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -876,7 +919,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     const bool tma_store = pl.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0;
     {
         // W as 8-byte elements: one k16-block plane is a row of 2N elements (n-major, 16 B per n), so the 128 n of a tile
-        // are 2048 contiguous bytes = 256 elements.  A box is 4 planes x 256 elements and lands as [4][128 n][16 B].
+        // are 2048 contiguous bytes = 256 elements.  A box is 8 planes x 256 elements and lands as [8][128 n][16 B].
         // (A byte-typed box with a 16-byte inner extent would make the copy engine issue 512 16-byte rows per stage.)
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N) * 2, static_cast<cuuint64_t>(K / 16)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 16};
@@ -888,10 +931,10 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
     }
     {
-        // A as (K, M) fp16; a box is 64 k x (tokens per CTA), 128-byte swizzle, rows beyond M read as zero.
+        // A as (K, M) fp16; a box is one sub-tile, 64 k x (tokens per CTA), 128-byte swizzle; rows beyond M and k beyond K read as zero.
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-        const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(pl.tn / pl.cg)};
+        const cuuint32_t box[2] = {kSubK, static_cast<cuuint32_t>(pl.tn / pl.cg)};
         const cuuint32_t estr[2] = {1, 1};
         const CUresult r = encode(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
