@@ -155,8 +155,10 @@ quantize_prepack_kernel(const void* __restrict__ src, const float* __restrict__ 
     constexpr int kIters = kQRows * kVecPerRow / 256;      // 4 or 2
     __shared__ __align__(16) uint8_t tile[kQK / 16][kQRows + 1][16];   // +1 row: conflict-free 16-byte access both ways
 
-    const int n0 = blockIdx.y * kQRows;
-    const int k0 = blockIdx.x * kQK;
+    // Blocks walk the weight from its end to its start: the amax pass that ran just before read it start to end, so the
+    // tail is what is still in L2 and the second read of that part costs no HBM traffic.
+    const int n0 = (gridDim.y - 1 - blockIdx.y) * kQRows;
+    const int k0 = (gridDim.x - 1 - blockIdx.x) * kQK;
     const bool use_pm = (kSrc == FEATHER_SRC_FP32 && premul != nullptr);
     const float pm = use_pm ? __ldg(premul) : 1.0f;
     // inv_scale = (1.0 / scale).to(x.dtype)

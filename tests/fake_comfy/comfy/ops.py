@@ -44,7 +44,9 @@ def cast_bias_weight(s, input=None, dtype=None, device=None, bias_dtype=None, of
     weight = s.weight
     is_quantized = hasattr(weight, "_qdata")
     if is_quantized:
-        weight = weight.to(device=device) if weight.device != torch.device(device) else weight
+        # the wrapper's own .device is not reliable after nn.Module.to(); look at the packed data
+        if weight._qdata.device != torch.device(device):
+            weight = type(weight)(weight._qdata.to(device), weight._layout_cls, weight._params.to_device(device))
     else:
         weight = weight.to(device=device, dtype=dtype)
     for fn in getattr(s, "weight_function", []):

@@ -100,7 +100,7 @@ def test_lora_merge_round_trip(ops_mod, quant_mod, cuda_dev):
     w = (rng.standard_normal((N, K), dtype=np.float32) / 11).astype(np.float32)
     lin = _make_linear(ops_mod, K, N, torch.bfloat16, {"weight": torch.from_numpy(w)}).to(cuda_dev)
     q0, s0 = fo.make_feather_quantized_weight(w, "fp32", None)
-    deq = lin.convert_weight(lin.weight)
+    deq = lin.convert_weight(lin.weight).to(cuda_dev)      # the packed data stays where the checkpoint was loaded (host)
     assert deq.dtype == torch.bfloat16 and deq.shape == (N, K)
     assert np.array_equal(from_torch(deq), fo.layout_dequantize(q0, s0, "bf16"))
     delta = fo.f32_to_bf16_bits((rng.standard_normal((N, K), dtype=np.float32) / 50).astype(np.float32))
