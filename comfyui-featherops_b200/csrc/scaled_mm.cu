@@ -49,6 +49,9 @@ constexpr int kMaxStages = 16;
 // Split-K workspace: a fixed-size block of tile counters first (so the counters of any launch only ever overlap the counters of
 // another, which every launch leaves at zero), then the fp32 partial tiles.
 constexpr size_t kCounterBytes = 65536;
+#ifndef FEATHER_STATIC_SCRATCH_BYTES
+#define FEATHER_STATIC_SCRATCH_BYTES (8u << 20)
+#endif
 
 __host__ __device__ constexpr int pow2_at_least(int x) {
     int p = 32;
@@ -1019,6 +1022,68 @@ extern "C" int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const
     const int st = scaled_mm_impl(a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K, N, output_dtype, &v,
                                   nullptr, 0, nullptr, static_cast<cudaStream_t>(stream));
     return st == FEATHER_OK ? 1 : 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory: the split-K scratch is a fixed array that is part of
+// this library's device image.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = FEATHER_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address a kernel can use comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static int static_scratch_of_current_device(void** out) {
+    static std::mutex mu;
+    static void* cached[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return set_error(FEATHER_ERR_NO_DEVICE, "no current CUDA device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return set_error(FEATHER_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return FEATHER_OK;
+}
+
+extern "C" size_t feather_scaled_mm_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c, int64_t M,
+                                        int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
+                                        int* status_dev, feather_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
+    if (M == 0) return FEATHER_OK;
+    const int sms = sm_count_of_current_device();
+    if (sms <= 0) return set_error(FEATHER_ERR_NO_DEVICE, "no CUDA device");
+    Plan pl;
+    if (!make_plan(M, N, K, variant, 0, false, sms, &pl)) return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
+    if (pl.ws_bytes > kStaticScratchBytes)
+        return set_error(FEATHER_ERR_WORKSPACE,
+                         "this shape needs %zu bytes of split-K scratch but the built-in scratch holds %zu; use feather_scaled_mm_ex with "
+                         "a caller-provided workspace, or pass a variant with a smaller split_k",
+                         pl.ws_bytes, kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (int st = static_scratch_of_current_device(&scratch)) return st;
+    feather_mm_variant fixed{};
+    fixed.tokens_tile = pl.tn;
+    fixed.cta_pair = pl.cg;
+    fixed.split_k = pl.splits;
+    fixed.transform_groups = pl.tg;
+    fixed.max_ctas = pl.max_ctas;
+    if (pl.splits > 1) {
+        // Every call shares the array and it keeps the previous call's contents.  Only the tile counters have to start at
+        // zero; partial tiles are fully written before they are read.
+        const size_t counter_bytes = static_cast<size_t>(pl.tiles_n) * pl.tiles_t * pl.cg * sizeof(int);
+        const cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, stream);
+        if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "clearing the tile counters failed: %s", cudaGetErrorString(e));
+    }
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, &fixed, scratch, kStaticScratchBytes, status_dev, stream);
 }
 
 extern "C" size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant) {

@@ -30,6 +30,8 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_ex",
     "feather_scaled_mm_workspace_bytes",
     "feather_scaled_mm_choose",
+    "feather_scaled_mm_static",
+    "feather_scaled_mm_static_scratch_bytes",
     "feather_quantize_prepack",
     "feather_prepack_bytes",
     "feather_unprepack_bytes",
@@ -86,6 +88,10 @@ def load_library():
         lib.feather_scaled_mm_workspace_bytes.restype = sz
         lib.feather_scaled_mm_choose.argtypes = [i64, i64, i64, sz, ctypes.POINTER(MMVariant)]
         lib.feather_scaled_mm_choose.restype = ci
+        lib.feather_scaled_mm_static.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
+        lib.feather_scaled_mm_static.restype = ci
+        lib.feather_scaled_mm_static_scratch_bytes.argtypes = []
+        lib.feather_scaled_mm_static_scratch_bytes.restype = sz
         lib.feather_quantize_prepack.argtypes = [vp, ci, vp, i64, i64, ci, vp, vp, vp, vp]
         lib.feather_quantize_prepack.restype = ci
         lib.feather_prepack_bytes.argtypes = [vp, i64, i64, ci, vp, vp]
@@ -250,6 +256,28 @@ def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
         )
     _check(status, "feather_scaled_mm_ex")
     return c
+
+
+def scaled_mm_static_into(a, b_prepacked, scale, bias, c, variant=None):
+    """Same result as scaled_mm_into through `feather_scaled_mm_static`: the entry point for callers that cannot allocate
+    device memory, whose split-K scratch is a fixed array inside the library.  Raises FeatherNativeError (status 3) when the
+    shape needs more scratch than the array holds."""
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, c)
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    st = status_word_for(dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_scaled_mm_static(
+            _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), M, N, K, c.stride(0), _OUT_CODE[c.dtype],
+            ctypes.byref(variant) if variant is not None else None, _ptr(st), _stream_ptr(dev),
+        )
+    _check(status, "feather_scaled_mm_static")
+    return c
+
+
+def static_scratch_bytes():
+    return int(load_library().feather_scaled_mm_static_scratch_bytes())
 
 
 def launch_scaled_mm_reference_abi(a, b_prepacked, scale, bias, c, cfg=(1, 8, 4, 8, 2), b_dtype=1):

@@ -102,6 +102,26 @@ FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, 
  * names an unshipped split-k branch), so its launcher has no scratch argument (kernel/hip/hip_kernel.cu:564-582). */
 FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant);
 
+/* For callers that cannot allocate device memory themselves - code running inside a CUDA-graph capture or a host
+ * callback, plugins that are handed pointers by an allocator they do not own, or C programs that want to link the
+ * library and call one function without managing a workspace.  Same arguments and results as feather_scaled_mm_ex, minus
+ * the workspace: the split-K scratch is a fixed array of feather_scaled_mm_static_scratch_bytes() bytes (8 MiB) inside
+ * the library's device image, so every GPU that loads the library holds those bytes until the process exits.
+ *   - Shapes whose chosen variant needs more scratch than that are rejected with FEATHER_ERR_WORKSPACE (the message says
+ *     how much is needed); pass a variant with a smaller split_k, or use feather_scaled_mm_ex.
+ *   - The call allocates and frees nothing.  The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps what the previous call left there; the call clears the tile
+ *     counters it is about to use on `stream` before launching.  Two calls that can overlap on the GPU (different
+ *     streams, no dependency) would race on it: serialise them or use feather_scaled_mm_ex with separate workspaces.
+ * This entry point has no counterpart in the reference. */
+FEATHER_API int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c,
+                                         int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype,
+                                         const feather_mm_variant* variant, int* status_dev, feather_stream_t stream);
+
+/* Size in bytes of the built-in scratch used by feather_scaled_mm_static.  No counterpart in the reference. */
+FEATHER_API size_t feather_scaled_mm_static_scratch_bytes(void);
+
 /* Writes the variant the library would choose for (M,N,K) on the current device into *out.
  * Stands in for the autotuner of kernel/hip/utils.py:192-223 (`old_autotune`). */
 FEATHER_API int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t workspace_bytes, feather_mm_variant* out);
