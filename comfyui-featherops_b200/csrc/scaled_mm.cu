@@ -766,6 +766,51 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Encoded tensor maps are cached (a small direct-mapped table): encoding three maps costs more host time than a
+// small-M kernel runs.  The key holds everything the encoding depends on, so a changed pointer or shape is a miss.
+struct TmapKey {
+    const void* ptr;
+    uint64_t d0, d1, stride;
+    uint32_t b0, b1;
+    int kind, device;
+    bool operator==(const TmapKey& o) const {
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 && kind == o.kind && device == o.device;
+    }
+};
+static CUresult cached_tmap(EncodeTiledFn encode, CUtensorMap* out, int kind, CUtensorMapDataType dtype, const void* ptr, uint64_t d0, uint64_t d1,
+                            uint64_t stride_bytes, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz, CUtensorMapL2promotion promo) {
+    constexpr int kSlots = 64;
+    static std::mutex mu;
+    static TmapKey keys[kSlots];
+    static CUtensorMap maps[kSlots];
+    static bool used[kSlots];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const TmapKey key{ptr, d0, d1, stride_bytes, b0, b1, kind, dev};
+    const size_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull + d0 * 31 + d1 * 17 + b1 * 7 + kind;
+    const int slot = static_cast<int>((h >> 20) % kSlots);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (used[slot] && keys[slot] == key) {
+            *out = maps[slot];
+            return CUDA_SUCCESS;
+        }
+    }
+    const cuuint64_t dims[2] = {d0, d1};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {b0, b1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, promo,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lock(mu);
+        keys[slot] = key;
+        maps[slot] = *out;
+        used[slot] = true;
+    }
+    return r;
+}
+
 static int sm_count_of_current_device() {
     static std::mutex mu;
     static int cached[64];
@@ -800,9 +845,9 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (!valid_tn(tn)) return false;
     int cg = v ? v->cta_pair : 0;
-    if (cg == 0) cg = (M > 128 && N >= 2 * kBW) ? 2 : 1;   // CTA pairs halve the token-tile traffic per SM; small M is bound by the weight stream
+    // CTA pairs halve the token-tile traffic per SM (large M) and the MMAs issued per weight byte (small M)
+    if (cg == 0) cg = (N >= 2 * kBW) ? 2 : 1;
     if (cg != 1 && cg != 2) return false;
-    if (cg == 2 && tn < 32) return false;   // each CTA of a pair loads tn/2 token rows, at least one 8-row swizzle group x2
     pl.tn = tn;
     pl.cg = cg;
     pl.tg = v ? v->transform_groups : 0;
@@ -816,12 +861,19 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     int splits = v ? v->split_k : 0;
     if (splits == 0) {
         splits = 1;
-        if (tiles < clusters && pl.total_kb >= 8) {
-            // aim at >= 2 work units per cluster, keep at least 4 stages (512 k) per slice
-            int want = static_cast<int>((2LL * clusters + tiles - 1) / tiles);
-            int cap = pl.total_kb / 4;
-            splits = want < cap ? want : cap;
-            if (splits < 1) splits = 1;
+        if (tiles < 2 * clusters && pl.total_kb >= 4) {
+            // Pick the K split that minimises (rounds of work units over the clusters) x (stages per unit + a fixed per-unit
+            // cost of about three stage times for the drain, the partial tile and the hand-over).
+            long long best = -1;
+            for (int sp = 1; sp <= pl.total_kb / 2 && sp <= 32; ++sp) {
+                const long long rounds = (tiles * sp + clusters - 1) / clusters;
+                const long long per_unit = (pl.total_kb + sp - 1) / sp + (sp > 1 ? 3 : 1);
+                const long long cost = rounds * per_unit;
+                if (best < 0 || cost < best) {
+                    best = cost;
+                    splits = sp;
+                }
+            }
         }
         const size_t per_split = static_cast<size_t>(tiles) * tn * kBW * cg * sizeof(float);
         const size_t counters = kCounterBytes;
@@ -880,9 +932,7 @@ template <int TN>
 static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const CUtensorMap& tc, const MmParams& p, int grid,
                              cudaStream_t s) {
     if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
-    if constexpr (TN >= 32)
-        return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
-    return cudaErrorInvalidValue;
+    return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
 }
 
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
@@ -924,35 +974,23 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         // W as 8-byte elements: one k16-block plane is a row of 2N elements (n-major, 16 B per n), so the 128 n of a tile
         // are 2048 contiguous bytes = 256 elements.  A box is 8 planes x 256 elements and lands as [8][128 n][16 B].
         // (A byte-typed box with a 16-byte inner extent would make the copy engine issue 512 16-byte rows per stage.)
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N) * 2, static_cast<cuuint64_t>(K / 16)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 16};
-        const cuuint32_t box[2] = {kBW * 2, kKSteps};
-        const cuuint32_t estr[2] = {1, 1};
-        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(b), dims, strides, box, estr,
-                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUresult r = cached_tmap(encode, &tmap_w, 0, CU_TENSOR_MAP_DATA_TYPE_UINT64, b, static_cast<uint64_t>(N) * 2,
+                                       static_cast<uint64_t>(K / 16), static_cast<uint64_t>(N) * 16, kBW * 2, kKSteps, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
     }
     {
         // A as (K, M) fp16; a box is one sub-tile, 64 k x (tokens per CTA), 128-byte swizzle; rows beyond M and k beyond K read as zero.
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-        const cuuint32_t box[2] = {kSubK, static_cast<cuuint32_t>(pl.tn / pl.cg)};
-        const cuuint32_t estr[2] = {1, 1};
-        const CUresult r = encode(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), dims, strides, box, estr,
-                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUresult r = cached_tmap(encode, &tmap_a, 1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                                       static_cast<uint64_t>(K) * 2, kSubK, static_cast<uint32_t>(pl.tn / pl.cg), CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with CUresult %d", static_cast<int>(r));
     }
-
     if (tma_store) {
         // C as (N, M) 16-bit with row pitch ldc; a box is 128 n x (up to 32) token rows, clipped at N and M
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * 2};
-        const cuuint32_t box[2] = {kBW, static_cast<cuuint32_t>(pl.tn < 32 ? pl.tn : 32)};
-        const cuuint32_t estr[2] = {1, 1};
-        const CUresult r = encode(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUresult r = cached_tmap(encode, &tmap_c, 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, c, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                                       static_cast<uint64_t>(ldc) * 2, kBW, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32), CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_NONE);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
     }
 
@@ -969,9 +1007,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.K = static_cast<int>(K);
     p.ldc = ldc;
     p.out_bf16 = output_dtype == FEATHER_OUT_BF16 ? 1 : 0;
-    if (const char* dbg = getenv("FEATHER_DEBUG_FLAGS")) p.debug = atoi(dbg);
+    // Both switches are read once per process.
+    static const int env_debug = [] { const char* e = getenv("FEATHER_DEBUG_FLAGS"); return e ? atoi(e) : 0; }();
+    static const bool env_stats = getenv("FEATHER_STATS") != nullptr;
+    p.debug = env_debug;
     // FEATHER_STATS=1: the caller's status buffer is at least 8 + 32*8 bytes and receives the cycle counters of CTA 0 after the status word
-    if (status_dev != nullptr && getenv("FEATHER_STATS") != nullptr) p.stats = reinterpret_cast<long long*>(status_dev + 2);
+    if (status_dev != nullptr && env_stats) p.stats = reinterpret_cast<long long*>(status_dev + 2);
     p.splits = pl.splits;
     p.tiles_n = pl.tiles_n;
     p.tiles_t = pl.tiles_t;
