@@ -709,12 +709,27 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     __threadfence();
                     const float* const tile_part = p.ws_partials + static_cast<long long>(w.tile) * p.splits * (TN * kTileCols);
                     if (n_ok && alive) {
+                        // Blocks of 8 token rows, alternating between the two warp groups.  The 8 loads of a slice are
+                        // independent (and the next slices' loads can be hoisted), the additions stay in slice order.
+                        const long long slice_stride = static_cast<long long>(TN) * kTileCols;
 #pragma unroll 1
-                        for (int c = grp; c < valid; c += 2) {
-                            float acc = 0.0f;
-                            for (int sp = 0; sp < p.splits; ++sp)
-                                acc += __ldcg(tile_part + static_cast<long long>(sp) * (TN * kTileCols) + c * kTileCols + col);
-                            c16[static_cast<long long>(w.tok0 + c) * p.ldc + n] = finish_value(acc, scale, out_bf16, has_bias, bias_bits);
+                        for (int c0 = grp * 8; c0 < valid; c0 += 16) {
+                            float acc[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll 4
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                float v[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    v[i] = (c0 + i < valid) ? __ldcg(tile_part + sp * slice_stride + (c0 + i) * kTileCols + col) : 0.0f;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[i] += v[i];
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (c0 + i < valid)
+                                    c16[static_cast<long long>(w.tok0 + c0 + i) * p.ldc + n] = finish_value(acc[i], scale, out_bf16, has_bias, bias_bits);
                         }
                     }
                 }
@@ -862,12 +877,16 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     if (splits == 0) {
         splits = 1;
         if (tiles < 2 * clusters && pl.total_kb >= 4) {
-            // Pick the K split that minimises (rounds of work units over the clusters) x (stages per unit + a fixed per-unit
-            // cost of about three stage times for the drain, the partial tile and the hand-over).
+            // Pick the K split that minimises (rounds of work units over the clusters) x (cycles per unit).  A stage costs its
+            // eight MMAs (an MMA has a floor of ~94 cycles whatever its width); a split unit also parks an fp32 partial tile
+            // and one unit per tile reads them all back, which grows with the tokens tile (measured: splitting 128-token
+            // tiles costs more than it balances).
+            const long long stage_cycles = tn * 4 > 750 ? tn * 4 : 750;
+            const long long split_cycles = 1500 + 48LL * tn;
             long long best = -1;
             for (int sp = 1; sp <= pl.total_kb / 2 && sp <= 32; ++sp) {
                 const long long rounds = (tiles * sp + clusters - 1) / clusters;
-                const long long per_unit = (pl.total_kb + sp - 1) / sp + (sp > 1 ? 3 : 1);
+                const long long per_unit = ((pl.total_kb + sp - 1) / sp) * stage_cycles + (sp > 1 ? split_cycles : 300);
                 const long long cost = rounds * per_unit;
                 if (best < 0 || cost < best) {
                     best = cost;
@@ -935,6 +954,9 @@ static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtens
     return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
 }
 
+int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                   int output_dtype, int sms, cudaStream_t stream);   // small_m.cu
+
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
                           int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant, void* workspace,
                           size_t workspace_bytes, int* status_dev, cudaStream_t stream) {
@@ -953,6 +975,14 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
 
     const int sms = sm_count_of_current_device();
     if (sms <= 0) return set_error(FEATHER_ERR_NO_DEVICE, "no CUDA device");
+    // Bandwidth-bound end (a few tokens): the register-streaming kernel, unless the caller pinned a tensor-memory variant.
+    const int which = variant ? variant->kernel : 0;
+    if (which != FEATHER_KERNEL_AUTO && which != FEATHER_KERNEL_TMEM && which != FEATHER_KERNEL_STREAM)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.kernel must be 0 (auto), 1 (tensor memory) or 2 (streaming)");
+    if (which == FEATHER_KERNEL_STREAM && M > 32) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel handles at most 32 tokens");
+    const bool pinned = variant && (variant->tokens_tile || variant->cta_pair || variant->split_k || variant->transform_groups);
+    if (which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 32))
+        return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, sms, stream);
     Plan pl;
     if (!make_plan(M, N, K, variant, workspace ? workspace_bytes : 0, true, sms, &pl))
         return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
@@ -1117,6 +1147,7 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
     fixed.split_k = pl.splits;
     fixed.transform_groups = pl.tg;
     fixed.max_ctas = pl.max_ctas;
+    fixed.kernel = FEATHER_KERNEL_TMEM;   // this entry point exists for the variant that needs scratch
     if (pl.splits > 1) {
         // Every call shares the array and it keeps the previous call's contents.  Only the tile counters have to start at
         // zero; partial tiles are fully written before they are read.
@@ -1145,5 +1176,6 @@ extern "C" int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t 
     out->split_k = pl.splits;
     out->transform_groups = pl.tg;
     out->max_ctas = 0;
+    out->kernel = M <= 32 ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
     return FEATHER_OK;
 }

@@ -51,10 +51,11 @@ class MMVariant(ctypes.Structure):
         ("split_k", ctypes.c_int),
         ("transform_groups", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
+        ("kernel", ctypes.c_int),
     ]
 
     def as_tuple(self):
-        return (self.tokens_tile, self.cta_pair, self.split_k, self.transform_groups, self.max_ctas)
+        return (self.tokens_tile, self.cta_pair, self.split_k, self.transform_groups, self.max_ctas, self.kernel)
 
 
 class FeatherNativeError(RuntimeError):
@@ -221,8 +222,11 @@ def read_stats(device):
 # ------------------------------------------------------------------------------------------------
 # GEMM
 # ------------------------------------------------------------------------------------------------
-def make_variant(tokens_tile=0, cta_pair=0, split_k=0, transform_groups=0, max_ctas=0):
-    return MMVariant(tokens_tile, cta_pair, split_k, transform_groups, max_ctas)
+KERNEL_AUTO, KERNEL_TMEM, KERNEL_STREAM = 0, 1, 2
+
+
+def make_variant(tokens_tile=0, cta_pair=0, split_k=0, transform_groups=0, max_ctas=0, kernel=0):
+    return MMVariant(tokens_tile, cta_pair, split_k, transform_groups, max_ctas, kernel)
 
 
 def choose_variant(M, N, K, workspace_bytes=_WORKSPACE_BYTES):

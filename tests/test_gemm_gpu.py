@@ -115,6 +115,42 @@ def test_variants_against_oracle(native, cuda_dev, M, N, K, out_dtype, variant, 
     assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}")
 
 
+STREAM_CASES = [
+    # (M, N, K, out_dtype, bias)
+    (1, 256, 512, "bf16", False),
+    (1, 13824, 1024, "bf16", True),
+    (5, 72, 48, "fp16", True),            # N not a multiple of the 8-column strip group, K = 3 k16-blocks for 16 warps
+    (16, 200, 1040, "fp16", True),
+    (16, 8, 16, "bf16", True),            # one strip, one k16-block
+    (17, 1000, 2048, "bf16", True),       # two token tiles
+    (32, 5120, 1024, "fp16", False),
+    (9, 13824, 320, "bf16", True),
+    (8, 5120, 2048, "bf16", True),        # up to 8 tokens: the weights-as-rows variant
+    (3, 104, 64, "fp16", True),
+    (7, 24, 16, "fp16", False),
+]
+
+
+@pytest.mark.parametrize("M,N,K,out_dtype,bias", STREAM_CASES)
+def test_streaming_kernel_against_oracle(native, cuda_dev, M, N, K, out_dtype, bias):
+    """The register-streaming kernel for M <= 32 (forced, and as the library's own choice)."""
+    a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 11 + N + K, bias=bias)
+    ref = fo.scaled_mm(a, bq, s, b, out_dtype, product="fp32")
+    forced = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_STREAM))
+    assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}")
+    auto = _run(native, cuda_dev, a, bq, s, b, out_dtype, None)
+    assert np.array_equal(auto, forced)
+    assert native.choose_variant(M, N, K).kernel == native.KERNEL_STREAM
+    tmem = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_TMEM))
+    assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}")
+
+
+def test_streaming_kernel_rejects_many_tokens(native, cuda_dev):
+    a, bq, s, b = _synthetic(40, 64, 64, "bf16", seed=2)
+    with pytest.raises(native.FeatherNativeError, match="at most 32 tokens"):
+        _run(native, cuda_dev, a, bq, s, b, "bf16", (0, 0, 0, 0, 0, native.KERNEL_STREAM))
+
+
 def test_split_k_workspace_is_reusable(native, cuda_dev):
     """Back-to-back split-K launches on one workspace: the tile counters must be back at zero after each."""
     a, bq, s, b = _synthetic(48, 384, 2048, "bf16", seed=3)

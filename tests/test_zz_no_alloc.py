@@ -54,7 +54,7 @@ def test_static_scratch_entry_with_library_chosen_variant(native, cuda_dev):
         got = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_dev)
         native.scaled_mm_static_into(A, B, S, None, got)
         ref = torch.empty_like(got)
-        native.scaled_mm_into(A, B, S, None, ref)
+        native.scaled_mm_into(A, B, S, None, ref, variant=native.make_variant(kernel=native.KERNEL_TMEM))   # same kernel family, library-chosen split
         native.check_device_status(cuda_dev)
         assert torch.equal(got.view(torch.int16), ref.view(torch.int16))
 
