@@ -111,6 +111,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-rows", type=int, default=2048)
+    ap.add_argument("--exchange", default="peer_store", choices=["peer_store", "all_gather"],
+                    help="N > 1: fused peer-store epilogue over symmetric memory, or NCCL all-gather + relayout")
     return ap.parse_args()
 
 
@@ -218,7 +220,7 @@ def run_ours(args):
         w = torch.randn((N, K), generator=g, device=dev, dtype=torch.float32) / K ** 0.5
         bq, s = native.quantize_prepack(w)      # loader path: fp32 in, scale = amax / 57344
         del w
-        lin = sharded.ColumnShardedLinear(bq, s.reshape(1), None, rank, world, dev)
+        lin = sharded.ColumnShardedLinear(bq, s.reshape(1), None, rank, world, dev, exchange=args.exchange)
         layers.append((a, lin, K, N))
     torch.cuda.synchronize()
 
@@ -307,7 +309,9 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp16xfp8e5m2->fp32", "data": "synthetic",
             "config": {"workload": desc, "out_dtype": out_dtype, "l2": "inputs larger than L2 (A and C are 335-906 MB per linear)",
-                       "parallelism": "single GPU" if world == 1 else f"weights sharded by output columns over {world} GPUs + NCCL all-gather of the output",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"weights sharded by output columns over {world} GPUs; " + ("each rank's epilogue TMA-stores its blocks into every rank's output over NVLink (fused exchange)"
+                                                                                      if args.exchange == "peer_store" else "NCCL all-gather of the output + relayout")),
                        "variant": args.variant or "auto"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         }
@@ -370,25 +374,45 @@ def run_smallm(args, native, dev):
             a = torch.randn((M, K), generator=g, device=dev).to(torch.float16)
             c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
             variant = native.make_variant(*[int(x) for x in args.variant.split(",")]) if args.variant else None
-            for _ in range(max(args.warmup, 3)):
+            def sweep():
                 for b in copies:
                     native.scaled_mm_into(a, b, s, None, c, variant=variant)
+
+            for _ in range(max(args.warmup, 3)):
+                sweep()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
             for _ in range(args.steps):
-                for b in copies:
-                    native.scaled_mm_into(a, b, s, None, c, variant=variant)
+                sweep()
             e1.record()
             torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (args.steps * len(copies))
+            us_eager = e0.elapsed_time(e1) * 1e3 / (args.steps * len(copies))
+            # the same launches replayed from a CUDA graph: kernel time without the host's per-call cost
+            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                sweep()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(5):
+                        sweep()
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (args.steps * 5 * len(copies))
             nbytes = 2 * M * K + K * N + 2 * M * N + 4
             v = native.choose_variant(M, N, K)
-            rows.append({"M": M, "K": K, "N": N, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
-                         "tflops": round(2.0 * M * N * K / us / 1e6, 2), "variant": v.as_tuple()})
+            rows.append({"M": M, "K": K, "N": N, "us": round(us, 2), "us_eager": round(us_eager, 2), "gbs": round(nbytes / us / 1e3, 1),
+                         "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3), "tflops": round(2.0 * M * N * K / us / 1e6, 2),
+                         "kernel": {1: "tensor-memory", 2: "streaming"}.get(v.kernel, "auto"), "variant": v.as_tuple()})
     native.check_device_status(dev)
     print(json.dumps({"metric": "GB/s fp16@fp8e5m2 scaled_mm at M<=128", "unit": "GB/s", "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
-                      "config": {"workload": "small-M sweep, 4 rotating weight copies (283 MB > L2)"}, "rows": rows}), flush=True)
+                      "config": {"workload": "small-M sweep, 4 rotating weight copies (283 MB > L2); us = CUDA-graph replay, us_eager = per-call launches"}, "rows": rows}), flush=True)
 
 
 def run_quant(args, native, dev):

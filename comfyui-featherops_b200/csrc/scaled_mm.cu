@@ -104,8 +104,17 @@ struct MmParams {
                    // TMEM loads, 16 = transform warps skip the upcast work; with 1 set: 32 = no proxy fence, 64 = no named barriers,
                    // 128 = no staging writes.  None of them changes the mbarrier protocol.
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
+    int n_dst;     // number of output buffers every tile is stored to (1, or one per GPU of a column-sharded linear)
     int splits;
     int tiles_n, tiles_t, num_units, total_kb;
+};
+
+constexpr int kMaxDst = 8;
+// One tensor map per destination of the output.  Destination 0 is the caller's own buffer; the others are the same
+// [M, ldc] buffer in the memory of peer GPUs (NVLink), so a column shard lands in every rank's full output without a
+// separate all-gather.  Stores only: no load ever reads peer memory here.
+struct OutMaps {
+    CUtensorMap m[kMaxDst];
 };
 
 struct Unit {
@@ -193,7 +202,7 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
 template <int TN, int CG, int TG>
 __global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 3), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_c, const MmParams p) {
+                 const __grid_constant__ OutMaps tmap_c, const MmParams p) {
     using C = Cfg<TN, CG>;
     constexpr int kAStages = C::kAStages;
     constexpr int kWStages = C::kWStages;
@@ -261,7 +270,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
     if (warp == kProducerWarp && lane == 0) {
         prefetch_tmap(&tmap_a);
-        if (p.tma_store) prefetch_tmap(&tmap_c);
+        if (p.tma_store)
+            for (int d = 0; d < p.n_dst; ++d) prefetch_tmap(&tmap_c.m[d]);
     }
     if (warp == kWProducerWarp && lane == 0) prefetch_tmap(&tmap_w);
     if (warp == kMmaWarp) {
@@ -635,7 +645,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         fence_proxy_async_smem();
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                         if (group_leader && !dry) {
-                            tma_store_2d(&tmap_c, out_buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
+                            for (int d = 0; d < p.n_dst; ++d)
+                                tma_store_2d(&tmap_c.m[d], out_buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
                             tma_store_commit();
                         }
                     }
@@ -915,7 +926,7 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
 }
 
 template <int TN, int CG, int TG>
-static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const CUtensorMap& tc, const MmParams& p, int grid,
+static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p, int grid,
                                   cudaStream_t stream) {
     using C = Cfg<TN, CG>;
     auto kernel = scaled_mm_kernel<TN, CG, TG>;
@@ -948,7 +959,7 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
 }
 
 template <int TN>
-static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const CUtensorMap& tc, const MmParams& p, int grid,
+static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p, int grid,
                              cudaStream_t s) {
     if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
     return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
@@ -959,7 +970,7 @@ int small_m_launch(const void* a, const uint8_t* w, const float* scale, const vo
 
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
                           int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant, void* workspace,
-                          size_t workspace_bytes, int* status_dev, cudaStream_t stream) {
+                          size_t workspace_bytes, int* status_dev, cudaStream_t stream, void* const* extra_dst = nullptr, int n_extra = 0) {
     if (a == nullptr || b == nullptr || c == nullptr) return set_error(FEATHER_ERR_BAD_ARGUMENT, "a, b_prepacked and c must not be null");
     if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
     if (K % 16 != 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "K must be divisible by 16");
@@ -981,8 +992,13 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.kernel must be 0 (auto), 1 (tensor memory) or 2 (streaming)");
     if (which == FEATHER_KERNEL_STREAM && M > 32) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel handles at most 32 tokens");
     const bool pinned = variant && (variant->tokens_tile || variant->cta_pair || variant->split_k || variant->transform_groups);
-    if (which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 32))
+    if (n_extra < 0 || n_extra > kMaxDst - 1) return set_error(FEATHER_ERR_BAD_ARGUMENT, "at most %d output buffers", kMaxDst);
+    for (int d = 0; d < n_extra; ++d)
+        if (extra_dst == nullptr || extra_dst[d] == nullptr || (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15u) != 0)
+            return set_error(FEATHER_ERR_BAD_ARGUMENT, "every output buffer must be non-null and 16-byte aligned");
+    if ((which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 32)) && n_extra == 0)
         return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, sms, stream);
+    if (which == FEATHER_KERNEL_STREAM) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer");
     Plan pl;
     if (!make_plan(M, N, K, variant, workspace ? workspace_bytes : 0, true, sms, &pl))
         return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
@@ -996,10 +1012,13 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return set_error(FEATHER_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
 
-    CUtensorMap tmap_w, tmap_a, tmap_c;
+    CUtensorMap tmap_w, tmap_a;
+    OutMaps tmap_c;
     memset(&tmap_c, 0, sizeof(tmap_c));
     // TMA stores need 16-byte aligned output rows; otherwise (odd ldc, split-K) the epilogue stores 2 bytes at a time
     const bool tma_store = pl.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0;
+    if (n_extra > 0 && !tma_store)
+        return set_error(FEATHER_ERR_UNSUPPORTED, "several output buffers need 16-byte aligned rows (ldc %% 8 == 0) and a variant without split-K");
     {
         // W as 8-byte elements: one k16-block plane is a row of 2N elements (n-major, 16 B per n), so the 128 n of a tile
         // are 2048 contiguous bytes = 256 elements.  A box is 8 planes x 256 elements and lands as [8][128 n][16 B].
@@ -1018,14 +1037,18 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     }
     if (tma_store) {
         // C as (N, M) 16-bit with row pitch ldc; a box is 128 n x (up to 32) token rows, clipped at N and M
-        const CUresult r = cached_tmap(encode, &tmap_c, 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, c, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                                       static_cast<uint64_t>(ldc) * 2, kBW, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32), CU_TENSOR_MAP_SWIZZLE_NONE,
-                                       CU_TENSOR_MAP_L2_PROMOTION_NONE);
-        if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
+        for (int d = 0; d <= n_extra; ++d) {
+            void* const dst = d == 0 ? c : extra_dst[d - 1];
+            const CUresult r = cached_tmap(encode, &tmap_c.m[d], 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, static_cast<uint64_t>(N),
+                                           static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, kBW, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32),
+                                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+            if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
+        }
     }
 
     MmParams p{};
     p.tma_store = tma_store ? 1 : 0;
+    p.n_dst = 1 + n_extra;
     p.scale = scale;
     p.bias = bias;
     p.c = c;
@@ -1079,6 +1102,18 @@ extern "C" int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, c
                                     feather_stream_t stream) {
     return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, workspace, workspace_bytes, status_dev,
                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* const* c_list_host,
+                                       int n_dst, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
+                                       int* status_dev, feather_stream_t stream) {
+    if (c_list_host == nullptr || n_dst < 1) return set_error(FEATHER_ERR_BAD_ARGUMENT, "c_list_host must hold at least one output buffer");
+    feather_mm_variant v{};
+    if (variant) v = *variant;
+    v.split_k = 1;                      // every rank must add the k-blocks in the same order, and the stores go through TMA
+    v.kernel = FEATHER_KERNEL_TMEM;
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c_list_host[0], M, N, K, ldc, output_dtype, &v, nullptr, 0, status_dev,
+                          static_cast<cudaStream_t>(stream), c_list_host + 1, n_dst - 1);
 }
 
 extern "C" int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_workspace_bytes",
     "feather_scaled_mm_choose",
     "feather_scaled_mm_static",
+    "feather_scaled_mm_multi",
     "feather_scaled_mm_static_scratch_bytes",
     "feather_quantize_prepack",
     "feather_prepack_bytes",
@@ -91,6 +92,8 @@ def load_library():
         lib.feather_scaled_mm_choose.restype = ci
         lib.feather_scaled_mm_static.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
         lib.feather_scaled_mm_static.restype = ci
+        lib.feather_scaled_mm_multi.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
+        lib.feather_scaled_mm_multi.restype = ci
         lib.feather_scaled_mm_static_scratch_bytes.argtypes = []
         lib.feather_scaled_mm_static_scratch_bytes.restype = sz
         lib.feather_quantize_prepack.argtypes = [vp, ci, vp, i64, i64, ci, vp, vp, vp, vp]
@@ -260,6 +263,28 @@ def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
         )
     _check(status, "feather_scaled_mm_ex")
     return c
+
+
+def scaled_mm_multi_into(a, b_prepacked, scale, bias, outputs, variant=None):
+    """One GEMM launch whose epilogue stores every output block to each tensor of `outputs` (same shape/strides; the first is on
+    a's device, the others may alias peer GPUs' memory).  Used by the column-sharded linear to fuse the exchange into the GEMM."""
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, outputs[0])
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    c0 = outputs[0]
+    for c in outputs:
+        if c.shape != c0.shape or c.stride() != c0.stride() or c.dtype != c0.dtype:
+            raise FeatherNativeError("all output buffers must have the same shape, strides and dtype")
+    ptrs = (ctypes.c_void_p * len(outputs))(*[c.data_ptr() for c in outputs])
+    st = status_word_for(dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_scaled_mm_multi(
+            _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), ptrs, len(outputs), M, N, K, c0.stride(0), _OUT_CODE[c0.dtype],
+            ctypes.byref(variant) if variant is not None else None, _ptr(st), _stream_ptr(dev),
+        )
+    _check(status, "feather_scaled_mm_multi")
+    return outputs[0]
 
 
 def scaled_mm_static_into(a, b_prepacked, scale, bias, c, variant=None):

@@ -101,6 +101,17 @@ FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, 
                          int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
                          void* workspace, size_t workspace_bytes, int* status_dev, feather_stream_t stream);
 
+/* Column-sharded linear over the GPUs of one box, exchange fused into the GEMM: the same launch as feather_scaled_mm_ex,
+ * but every finished output block is stored (TMA store) to each of the n_dst buffers in c_list_host - a HOST array of device
+ * pointers: entry 0 the caller's own [M, ldc] buffer (already offset to this rank's first column), the others the same position
+ * in the peer GPUs' buffers (peer-mapped addresses, e.g. from torch symmetric memory), reached over NVLink.  No load touches
+ * peer memory.  Needs 16-byte aligned rows (ldc % 8 == 0, aligned pointers); K is never split, so all ranks produce bitwise
+ * the single-GPU result.  The caller synchronises the ranks (a barrier after the launch) before anyone reads the outputs.
+ * The reference has no multi-GPU path; this entry point has no counterpart in the reference. */
+FEATHER_API int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias,
+                                        void* const* c_list_host, int n_dst, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype,
+                                        const feather_mm_variant* variant, int* status_dev, feather_stream_t stream);
+
 /* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K).  Pass the same
  * `variant` (or NULL) as to feather_scaled_mm_ex.  The reference's shipped kernel never splits K (README.md:31
  * names an unshipped split-k branch), so its launcher has no scratch argument (kernel/hip/hip_kernel.cu:564-582). */

@@ -248,6 +248,26 @@ def test_column_shard_writes_in_place(native, cuda_dev):
     assert np.array_equal(from_torch(C), full)
 
 
+def test_multi_destination_epilogue_on_one_gpu(native, cuda_dev):
+    """The fused-exchange launch with all destinations on one GPU: every buffer receives the block, bitwise equal to the
+    ordinary launch; column ranges of a wider buffer are written in place and nothing else is touched."""
+    a, bq, s, b = _synthetic(300, 256, 1024, "bf16", seed=12)
+    single = _run(native, cuda_dev, a, bq, s, b, "bf16", (256, 2, 1, 2, 0))
+    A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
+    S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+    Bi = to_torch(b, "bf16", cuda_dev)
+    wide = [torch.full((300, 768), 7.0, dtype=torch.bfloat16, device=cuda_dev) for _ in range(3)]
+    native.scaled_mm_multi_into(A, B, S, Bi, [w[:, 256:512] for w in wide])
+    native.check_device_status(cuda_dev)
+    for w in wide:
+        assert np.array_equal(from_torch(w[:, 256:512]), single)
+        assert bool((w[:, :256] == 7.0).all()) and bool((w[:, 512:] == 7.0).all())
+    with pytest.raises(native.FeatherNativeError, match="16-byte aligned rows"):
+        odd = [torch.empty((300, 250), dtype=torch.bfloat16, device=cuda_dev) for _ in range(2)]
+        a2, bq2, s2, _ = _synthetic(300, 250, 64, "bf16", seed=1, bias=False)
+        native.scaled_mm_multi_into(to_torch(a2, "fp16", cuda_dev), to_torch(bq2, "e5m2", cuda_dev), None, None, odd)
+
+
 @pytest.mark.parametrize("K,N", [(5120, 13824), (13824, 5120), (5120, 5120)])
 def test_full_size_wan_shapes_properties(native, cuda_dev, K, N):
     """M = 32768 Wan-14B linears.  The CPU oracle cannot do 4.6 TFLOP in seconds, so: rows sampled across the whole
