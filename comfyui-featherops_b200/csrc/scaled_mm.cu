@@ -29,6 +29,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/feather_b200.h"
 #include "host_util.h"
@@ -100,9 +101,6 @@ struct MmParams {
     int M, N, K;
     long long ldc;
     int out_bf16;
-    int debug;     // FEATHER_DEBUG_FLAGS, timing experiments only (results are wrong): 1 = epilogue skips stores, 2 = also skips
-                   // TMEM loads, 16 = transform warps skip the upcast work; with 1 set: 32 = no proxy fence, 64 = no named barriers,
-                   // 128 = no staging writes.  None of them changes the mbarrier protocol.
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
     int n_dst;     // number of output buffers every tile is stored to (1, or one per GPU of a column-sharded linear)
     int splits;
@@ -197,6 +195,25 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
     __half2 v = __floats2half2_rn(r0, r1);
     if (has_bias) v = __hadd2(v, *reinterpret_cast<const __half2*>(&bias2));
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Eight packed pairs at once with the dtype and bias decisions made at compile time: inside the unrolled loop there is no
+// branch, so the eight multiply -> convert -> add chains overlap instead of running one after the other.
+template <bool kBf16, bool kBias>
+__device__ __forceinline__ void convert8(const uint32_t (&v)[16], uint32_t (&h)[8], float scale, uint32_t bias2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float r0 = __uint_as_float(v[2 * j]) * scale, r1 = __uint_as_float(v[2 * j + 1]) * scale;
+        if constexpr (kBf16) {
+            __nv_bfloat162 x = __floats2bfloat162_rn(r0, r1);
+            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __nv_bfloat162*>(&bias2));
+            h[j] = *reinterpret_cast<const uint32_t*>(&x);
+        } else {
+            __half2 x = __floats2half2_rn(r0, r1);
+            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __half2*>(&bias2));
+            h[j] = *reinterpret_cast<const uint32_t*>(&x);
+        }
+    }
 }
 
 template <int TN, int CG, int TG>
@@ -356,6 +373,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
             }
         }
+        // Lanes 1..31 wait here, at a warp-level convergence point, until lane 0 is done.  Without it they run ahead to the
+        // block/cluster barrier of the teardown and sit there polling for the whole kernel, which slows every working warp.
+        __syncwarp();
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA, one lane)
         if (rank == 0 && lane == 0) {
@@ -468,6 +488,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
             }
         }
+        __syncwarp();   // as for the producers: the idle lanes wait for the issuing lane here, not at the teardown barrier
     } else if (warp >= kFirstTransformWarp) {
         // ------------------------------------------------------------------ e5m2 -> fp16 into TMEM
         const int q = warp & 3;
@@ -502,7 +523,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t src = smem_w + s * kWStageBytes + w_lane_off;
                 const uint32_t dst = tmem_wring + t_lane + t * kTColsPerStage;
-                if ((p.debug & 16) == 0) {
+                {
                     uint32_t x[kKSteps][4];
 #pragma unroll
                     for (int j = 0; j < kKSteps; ++j)
@@ -584,7 +605,6 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint16_t bias_bits = (has_bias && n_ok) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + n) : uint16_t(0);
             const uint32_t src = tmem_base + t_lane + a * TN;
             const int valid = p.M - w.tok0 < TN ? p.M - w.tok0 : TN;              // token columns of this tile that exist
-            const bool skip_loads = !alive || (p.debug & 2) != 0;
             // The accumulator goes back to the MMA warp as soon as this warp's last TMEM load of the tile has landed.
             bool released = false;
             auto release_acc = [&]() {
@@ -601,98 +621,119 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 }
             };
 
-            if (p.splits == 1) {
-                uint16_t* const c_col = c16 + static_cast<long long>(w.tok0) * p.ldc + n;
-                const bool direct_store = !staged && n_ok && alive && (p.debug & 1) == 0;
-                const bool dry = (p.debug & 1) != 0;                              // timing experiments: no store is issued
+            if (staged) {
+                // Staged path: each group of four warps fills its shared-memory buffer with kOutRows token rows of the
+                // CTA's 128 output columns and one thread hands the buffer to TMA.  The loop body is free of run-time
+                // switches (output type and bias are compile-time tags, chosen once per tile).
                 const bool odd = (lane & 1) != 0;
                 const uint32_t pick = odd ? 0x3276u : 0x5410u;
                 const uint32_t bias2 = static_cast<uint32_t>(bias_bits) * 0x00010001u;
                 const uint32_t lane_off = (col_local & ~1) * 2 + (odd ? kBW * 2 : 0);
-
-                // 16 accumulator columns (token rows c0 .. c0+15 of this tile) held in registers -> output.
-                // Staged path: lanes 2i and 2i+1 hold neighbouring output columns; each converts token pairs of its own
-                // column into packed words, swaps them with its neighbour and picks, with one byte permute, the 32-bit word
-                // {column 2i, column 2i+1} of one token row (even lane: the pair's first token, odd lane: the second).
-                // Sub-word shared-memory stores, and one fused convert-exchange-store loop, were both several times slower.
-                auto emit16 = [&](const uint32_t (&v)[16], int c0, uint32_t buf_rows) {
-                    if (staged) {
+                const int first = grp * kOutRows;                                  // this group's blocks: first, first + 2*kOutRows, ...
+                const int store_x = w.n0 + static_cast<int>(rank) * kBW;
+                auto drain = [&](auto bf16_tag, auto bias_tag) {
+                    constexpr bool kBf16 = decltype(bf16_tag)::value;
+                    constexpr bool kBias = decltype(bias_tag)::value;
+                    // 16 accumulator columns (token rows of this tile) held in registers -> staging buffer.  Lanes 2i and
+                    // 2i+1 hold neighbouring output columns; each converts token pairs of its own column into packed words,
+                    // swaps them with its neighbour and picks, with one byte permute, the 32-bit word {column 2i, column
+                    // 2i+1} of one token row (even lane: the pair's first token, odd lane: the second).  Sub-word
+                    // shared-memory stores, and one fused convert-exchange-store loop, were both several times slower.
+                    auto stage16 = [&](const uint32_t (&v)[16], uint32_t buf_rows) {
                         uint32_t h[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            h[j] = finish_pair(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), scale, out_bf16, has_bias, bias2);
+                        convert8<kBf16, kBias>(v, h, scale, bias2);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) h[j] = __byte_perm(h[j], __shfl_xor_sync(0xffffffffu, h[j], 1), pick);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) asm volatile("st.shared.u32 [%0], %1;" ::"r"(buf_rows + lane_off + 2 * j * (kBW * 2)), "r"(h[j]));
-                    } else if (direct_store) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (c0 + j < valid)
-                                c_col[static_cast<long long>(c0 + j) * p.ldc] = finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits);
-                        }
-                    }
-                };
-                // one block = kOutRows token rows = this group's staging buffer = one TMA store
-                auto block_begin = [&]() {
-                    if (staged) {
+                    };
+                    auto block_begin = [&]() {
                         if (group_leader) tma_store_wait_read<0>();              // the previous store of this group has read the buffer
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                    }
-                };
-                auto block_end = [&](int c0) {
-                    if (staged) {
+                    };
+                    auto block_end = [&](int c0) {
                         fence_proxy_async_smem();
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                        if (group_leader && !dry) {
-                            for (int d = 0; d < p.n_dst; ++d)
-                                tma_store_2d(&tmap_c.m[d], out_buf, w.n0 + static_cast<int>(rank) * kBW, w.tok0 + c0);
+                        if (group_leader) {
+                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&tmap_c.m[d], out_buf, store_x, w.tok0 + c0);
                             tma_store_commit();
                         }
-                    }
-                    ++st_chunks;
-                };
-                tw.start();
-                const int first = grp * kOutRows;                                  // this group's blocks: first, first + 2*kOutRows, ...
-                uint32_t va[16] = {}, vb[16] = {};
-                if (first < valid && !skip_loads) tmem_ld_32x32b_x16(src + first, va);
+                    };
+                    uint32_t va[16], vb[16];
+                    if (first < valid) tmem_ld_32x32b_x16(src + first, va);
 #pragma unroll 1
-                for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
-                    const int next = c0 + 2 * kOutRows;
-                    if constexpr (kOutRows == 16) {
-                        if (!skip_loads) tc_wait_ld();
-                        if (next < valid) {
-                            if (!skip_loads) tmem_ld_32x32b_x16(src + next, vb);   // vb doubles as the next block's buffer
-                        } else {
-                            release_acc();
-                        }
-                        block_begin();
-                        emit16(va, c0, out_buf);
-                        block_end(c0);
-                        if (next < valid) {
+                    for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
+                        const int next = c0 + 2 * kOutRows;
+                        if constexpr (kOutRows == 16) {
+                            tc_wait_ld();
+                            if (next < valid) {
+                                tmem_ld_32x32b_x16(src + next, vb);               // vb doubles as the next block's buffer
+                            } else {
+                                release_acc();
+                            }
+                            block_begin();
+                            stage16(va, out_buf);
+                            block_end(c0);
+                            if (next < valid) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) va[j] = vb[j];
-                        }
-                    } else {
-                        // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
-                        if (!skip_loads) {
+                                for (int j = 0; j < 16; ++j) va[j] = vb[j];
+                            }
+                        } else {
+                            // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
                             tc_wait_ld();
                             tmem_ld_32x32b_x16(src + c0 + 16, vb);
+                            block_begin();
+                            stage16(va, out_buf);
+                            tc_wait_ld();
+                            if (next < valid) {
+                                tmem_ld_32x32b_x16(src + next, va);
+                            } else {
+                                release_acc();
+                            }
+                            stage16(vb, out_buf + 16 * kBW * 2);
+                            block_end(c0);
                         }
-                        block_begin();
-                        emit16(va, c0, out_buf);
-                        if (!skip_loads) tc_wait_ld();
-                        if (next < valid) {
-                            if (!skip_loads) tmem_ld_32x32b_x16(src + next, va);
-                        } else {
-                            release_acc();
-                        }
-                        emit16(vb, c0 + 16, out_buf + 16 * kBW * 2);
-                        block_end(c0);
+                    }
+                    release_acc();                                                 // a group without any block in this tile
+                };
+                tw.start();
+                if (alive) {
+                    if (out_bf16) {
+                        if (has_bias) drain(std::true_type{}, std::true_type{});
+                        else drain(std::true_type{}, std::false_type{});
+                    } else {
+                        if (has_bias) drain(std::false_type{}, std::true_type{});
+                        else drain(std::false_type{}, std::false_type{});
+                    }
+                } else {
+                    // bystander: joins the group's two barriers per block and nothing else
+                    for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                     }
                 }
-                release_acc();                                                     // a group without any block in this tile
                 tw.stop(st_emit);
+                if (first < valid) st_chunks += (valid - first + 2 * kOutRows - 1) / (2 * kOutRows);
+            } else if (p.splits == 1) {
+                // Direct path (output rows that TMA cannot address: a row pitch that is not a multiple of 16 bytes)
+                uint16_t* const c_col = c16 + static_cast<long long>(w.tok0) * p.ldc + n;
+                if (alive) {
+#pragma unroll 1
+                    for (int c0 = grp * 16; c0 < valid; c0 += 32) {
+                        uint32_t v[16];
+                        tmem_ld_32x32b_x16(src + c0, v);
+                        tc_wait_ld();
+                        if (c0 + 32 >= valid) release_acc();
+                        if (n_ok) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (c0 + j < valid)
+                                    c_col[static_cast<long long>(c0 + j) * p.ldc] = finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits);
+                            }
+                        }
+                    }
+                }
+                release_acc();
             } else {
                 // split-K: park this slice's fp32 partial, then the last slice to arrive reduces in slice order
                 float* const part = p.ws_partials + (static_cast<long long>(w.tile) * p.splits + w.split) * (TN * kTileCols);
@@ -1060,10 +1101,8 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.K = static_cast<int>(K);
     p.ldc = ldc;
     p.out_bf16 = output_dtype == FEATHER_OUT_BF16 ? 1 : 0;
-    // Both switches are read once per process.
-    static const int env_debug = [] { const char* e = getenv("FEATHER_DEBUG_FLAGS"); return e ? atoi(e) : 0; }();
+    // Read once per process.
     static const bool env_stats = getenv("FEATHER_STATS") != nullptr;
-    p.debug = env_debug;
     // FEATHER_STATS=1: the caller's status buffer is at least 8 + 32*8 bytes and receives the cycle counters of CTA 0 after the status word
     if (status_dev != nullptr && env_stats) p.stats = reinterpret_cast<long long*>(status_dev + 2);
     p.splits = pl.splits;
