@@ -416,7 +416,8 @@ def run_smallm(args, native, dev):
 
 
 def run_quant(args, native, dev):
-    """quantise + prepack of one Wan ffn weight (13824 x 5120): GB/s of one-pass algorithmic bytes (read s*N*K, write N*K)."""
+    """quantise + prepack of one Wan ffn weight (13824 x 5120): GB/s of one-pass bytes (read s*N*K, write N*K) and of the
+    two-pass bytes the amax dependency imposes on a weight larger than L2 (read 2*s*N*K, write N*K)."""
     peaks = load_peaks()
     N, K = 13824, 5120
     rows = []
@@ -432,8 +433,10 @@ def run_quant(args, native, dev):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / args.steps
-        nbytes = (size + 1) * N * K
-        rows.append({"src": str(dt).replace("torch.", ""), "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3)})
+        nbytes = (size + 1) * N * K          # one pass: what a weight that stays in L2 between the two kernels would cost
+        nbytes2 = (2 * size + 1) * N * K     # two passes: amax over the whole weight must finish before any byte is quantised
+        rows.append({"src": str(dt).replace("torch.", ""), "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                     "gbs_two_pass": round(nbytes2 / us / 1e3, 1), "frac_hbm_two_pass": round(nbytes2 / us / 1e3 / peaks["hbm_gbs"], 3)})
     print(json.dumps({"metric": "GB/s quantise+prepack (13824x5120)", "unit": "GB/s", "peak_hbm_gbs": peaks["hbm_gbs"], "rows": rows}), flush=True)
 
 

@@ -43,6 +43,23 @@ __device__ __forceinline__ uint32_t f32_to_e5m2_bits(float f) {
     return r | sign;
 }
 
+// Four fp32 -> four e5m2 bytes (element i in byte i).  The hardware conversion rounds to nearest even like torch but
+// saturates, so it is used only where torch's result is finite: |x| < 61440 (61440 is the tie between 57344, the largest
+// finite e5m2, and 65536, which torch rounds to inf).  A word holding anything at or above that, or a NaN, takes the
+// software path; as unsigned integers, |x| bit patterns order like the values and every NaN is above inf.
+__device__ __forceinline__ uint32_t f32x4_to_e5m2_word(float x0, float x1, float x2, float x3) {
+    const uint32_t a0 = __float_as_uint(x0) & 0x7FFFFFFFu, a1 = __float_as_uint(x1) & 0x7FFFFFFFu;
+    const uint32_t a2 = __float_as_uint(x2) & 0x7FFFFFFFu, a3 = __float_as_uint(x3) & 0x7FFFFFFFu;
+    const uint32_t m = max(max(a0, a1), max(a2, a3));
+    if (m >= 0x47700000u)
+        return f32_to_e5m2_bits(x0) | (f32_to_e5m2_bits(x1) << 8) | (f32_to_e5m2_bits(x2) << 16) | (f32_to_e5m2_bits(x3) << 24);
+    uint16_t lo, hi;
+    // cvt...x2 d, a, b: a -> upper byte, b -> lower byte
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(x1), "f"(x0));
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(x3), "f"(x2));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
 template <int kSrc>
 struct Src;
 template <>
@@ -177,14 +194,14 @@ quantize_prepack_kernel(const void* __restrict__ src, const float* __restrict__ 
             uint32_t packed[kPer / 4];
 #pragma unroll
             for (int w = 0; w < kPer / 4; ++w) {
-                uint32_t word = 0;
+                float y[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float v = x[4 * w + j];
                     if (use_pm) v = __fmul_rn(v, pm);
-                    word |= f32_to_e5m2_bits(S::mul(v, inv)) << (8 * j);
+                    y[j] = S::mul(v, inv);
                 }
-                packed[w] = word;
+                packed[w] = f32x4_to_e5m2_word(y[0], y[1], y[2], y[3]);
             }
             const int kk = cv * kPer;                       // k offset inside the tile
             uint8_t* const cell = &tile[kk / 16][row][kk % 16];

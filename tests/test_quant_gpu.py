@@ -58,6 +58,24 @@ def test_fp32_random_bit_patterns(native, cuda_dev):
     assert np.array_equal(cases.canonical_e5m2(from_torch(q)), cases.canonical_e5m2(ref))
 
 
+def test_fp32_rounding_boundaries(native, cuda_dev):
+    """Every e5m2 code, every midpoint between neighbouring codes (the round-to-nearest-even ties) and the fp32 values
+    just below and above each, both signs; includes the subnormal codes and the 57344 / 61440 / 65536 overflow edge."""
+    codes = np.arange(0, 0x7D, dtype=np.uint16)                      # 0 .. inf
+    vals = (codes << 8).view(np.float16).astype(np.float32)          # e5m2 code -> value (top byte of fp16)
+    vals[-1] = 65536.0                                               # where inf would sit if e5m2 continued
+    mid = ((vals[:-1].astype(np.float64) + vals[1:].astype(np.float64)) / 2).astype(np.float32)
+    pts = np.concatenate([vals, mid, np.nextafter(mid, np.float32(0)), np.nextafter(mid, np.float32(np.inf)),
+                          np.nextafter(vals[1:], np.float32(0)), np.nextafter(vals, np.float32(np.inf))])
+    pts = np.concatenate([pts, -pts]).astype(np.float32)
+    pad = (-pts.size) % 64
+    pats32 = np.concatenate([pts, np.zeros(pad, np.float32)]).reshape(-1, 64)
+    q, _ = native.quantize_prepack(to_torch(pats32, "fp32", cuda_dev), scale=torch.tensor(1.0, device=cuda_dev))
+    with np.errstate(all="ignore"):
+        ref, _ = fo.layout_quantize(pats32, "fp32", scale=1.0)
+    assert np.array_equal(cases.canonical_e5m2(from_torch(q)), cases.canonical_e5m2(ref))
+
+
 def test_prepack_kn_matches_reference_helper(hip_kernel, cuda_dev):
     b = torch.randint(0, 256, (160, 72), dtype=torch.uint8, device=cuda_dev)
     got = from_torch(hip_kernel.prepack_b_for_scaled_mm(b.view(torch.float8_e5m2)))
