@@ -95,8 +95,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    // Fast path: try_wait itself blocks for a hardware-defined interval, so a short run of attempts covers every
-    // ordinary wait without touching the timer.  (A nanosleep back-off here costs hundreds of cycles per wake-up.)
+    // A phase that is already complete is seen by test_wait in about 15 cycles; try_wait takes 70-150 even then.
+    if (mbar_test_wait(bar, parity)) return true;
+    // try_wait itself blocks for a hardware-defined interval, so a short run of attempts covers every ordinary wait
+    // without touching the timer.  (A nanosleep back-off here costs hundreds of cycles per wake-up.)
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -112,12 +114,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // Whole-warp form: lane 0 polls, the other lanes sleep at the warp barrier, then every lane observes the
-// completed phase itself (one try_wait that succeeds at once) so each thread has its own acquire.
+// completed phase itself (one test_wait that succeeds at once) so each thread has its own acquire.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
     bool ok = true;
     if (lane == 0) ok = mbar_wait(bar, parity, abort_flag);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (ok) ok = mbar_try_wait(bar, parity);
+    if (ok) ok = mbar_test_wait(bar, parity);
     return __all_sync(0xffffffffu, ok);
 }
 
@@ -145,6 +147,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster_addr, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
 

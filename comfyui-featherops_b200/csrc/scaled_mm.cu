@@ -67,20 +67,29 @@ struct Cfg {
     static constexpr int kTokLoad = TN / CG;              // token rows this CTA loads per stage
     static constexpr int kASubBytes = kTokLoad * 128;     // one sub-tile: 64 fp16 per row
     static constexpr int kAStageBytes = kASubBytes * kSubTiles;
-    static constexpr int kAccs = (TN <= 192) ? 2 : 1;     // accumulator buffers in TMEM (two: the epilogue overlaps the next tile)
-    static constexpr int kAccCols = kAccs * TN;
+    // One thread can issue a tcgen05.mma about every 55-70 cycles, whatever its size, so for tiles of at most 128 tokens
+    // (64 cycles of tensor pipe per MMA) a single issuer is the bottleneck.  Those tiles use two issuing threads in two
+    // warps: even k-blocks of a tile go to issuer 0, odd ones to issuer 1, each with an accumulator of its own (the
+    // partial sums are added in the epilogue, always in the same order, so results stay reproducible).
+    static constexpr int kIssuers = (TN <= 128) ? 2 : 1;
+    // Tile buffers in TMEM: with two, the epilogue of one tile overlaps the MMAs of the next.
+    static constexpr int kAccs = (TN <= 64 || TN == 192) ? 2 : 1;
+    static constexpr int kAccCols = kAccs * kIssuers * TN;
+    static_assert(kAccCols <= 384, "accumulator columns");
     static constexpr int kTStagesRaw = (512 - kAccCols) / kTColsPerStage;
     static constexpr int kTStages = kTStagesRaw > kMaxTStages ? kMaxTStages : kTStagesRaw;   // TMEM ring depth
-    static constexpr int kTmemCols = pow2_at_least(kAccCols + kTStages * kTColsPerStage);
+    static constexpr int kTmemCols = pow2_at_least(kAccCols + kTStages * kTColsPerStage);   // the ring may use fewer (kAStages) slots
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kOutRows = TN < 32 ? TN : 32;                   // token rows per output staging buffer
     static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [rows][128 n] 16-bit
     static constexpr int kOutBytes = 2 * kOutBufBytes;                   // double buffered
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
-    // Two independent rings: token tiles (freed when the MMAs that read them retire) and raw weight bytes (freed as soon as
-    // the transform warps have read them).  The weight ring is one stage deeper so weights arrive ahead of the upcast.
-    static constexpr int kAStagesRaw = (kSmemBudget - kWStageBytes) / (kAStageBytes + kWStageBytes);
-    static constexpr int kAStages = kAStagesRaw > 12 ? 12 : kAStagesRaw;
+    // One operand ring for the MMA warp: slot i holds a token tile in shared memory and the matching upcast weights in
+    // tensor memory, so the single issuing thread waits on one barrier and commits to one barrier per k-block (its
+    // instruction count per k-block bounds the speed of every tile narrower than 256 tokens).  The raw weight bytes have a
+    // ring of their own (freed as soon as the transform warps have read them) that takes the rest of shared memory.
+    static constexpr int kAStagesRaw = (kSmemBudget - 2 * kWStageBytes) / kAStageBytes;
+    static constexpr int kAStages = kAStagesRaw > kTStages ? kTStages : kAStagesRaw;
     static constexpr int kWStagesRaw = (kSmemBudget - kAStages * kAStageBytes) / kWStageBytes;
     static constexpr int kWStages = kWStagesRaw > kMaxStages ? kMaxStages : kWStagesRaw;
     static constexpr int kSmemBytes = kAStages * kAStageBytes + kWStages * kWStageBytes + kOutBytes + kBarrierBytes + 1024;
@@ -101,6 +110,7 @@ struct MmParams {
     int M, N, K;
     long long ldc;
     int out_bf16;
+    int a3d;       // 1: the token tensor map is the 3-D form (64 k, M, K/64): one copy per k-block
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
     int n_dst;     // number of output buffers every tile is stored to (1, or one per GPU of a column-sharded linear)
     int splits;
@@ -217,40 +227,39 @@ __device__ __forceinline__ void convert8(const uint32_t (&v)[16], uint32_t (&h)[
 }
 
 template <int TN, int CG, int TG>
-__global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 3), 1)
+__global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ OutMaps tmap_c, const MmParams p) {
     using C = Cfg<TN, CG>;
-    constexpr int kAStages = C::kAStages;
+    constexpr int kStages = C::kAStages;                                  // operand ring depth (token tile + upcast weights per slot)
     constexpr int kWStages = C::kWStages;
-    constexpr int kTStages = C::kTStages;
     constexpr int kAccs = C::kAccs;
     constexpr int kFirstTransformWarp = kEpilogueWarps;
     constexpr int kProducerWarp = kEpilogueWarps + 4 * TG;
     constexpr int kMmaWarp = kProducerWarp + 1;
     constexpr int kWProducerWarp = kProducerWarp + 2;
+    constexpr int kIssuers = C::kIssuers;
+    constexpr int kMma2Warp = kProducerWarp + 3;                          // second issuer (exists only when kIssuers == 2)
     constexpr bool kPair = (CG == 2);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const uint32_t smem_a = smem_base;                                   // [kAStages][kAStageBytes]
-    const uint32_t smem_w = smem_base + kAStages * C::kAStageBytes;      // [kWStages][kWStageBytes]
-    constexpr int kRingBytes = kAStages * C::kAStageBytes + kWStages * kWStageBytes;
+    const uint32_t smem_a = smem_base;                                   // [kStages][kAStageBytes]
+    const uint32_t smem_w = smem_base + kStages * C::kAStageBytes;       // [kWStages][kWStageBytes]
+    constexpr int kRingBytes = kStages * C::kAStageBytes + kWStages * kWStageBytes;
     const uint32_t smem_out = smem_base + kRingBytes;                    // [2][kOutRows][128] 16-bit output staging
     const uint32_t bar_base = smem_out + C::kOutBytes;                   // barrier block
     uint8_t* const bar_gen = smem_gen + kRingBytes + C::kOutBytes;
 
     const uint32_t bar_wfull = bar_base;                                 // [kWStages] weight bytes landed
     const uint32_t bar_wempty = bar_wfull + 8 * kMaxStages;              // [kWStages] weight bytes read by the 4 transform warps
-    const uint32_t bar_afull = bar_wempty + 8 * kMaxStages;              // [kAStages] token tile landed (both CTAs of a pair)
-    const uint32_t bar_aempty = bar_afull + 8 * kMaxStages;              // [kAStages] token tile no longer read by any MMA
-    const uint32_t bar_tfull = bar_aempty + 8 * kMaxStages;              // [kTStages]
-    const uint32_t bar_tempty = bar_tfull + 8 * kMaxTStages;             // [kTStages]
-    const uint32_t bar_accfull = bar_tempty + 8 * kMaxTStages;           // [2]
+    const uint32_t bar_full = bar_wempty + 8 * kMaxStages;               // [kStages] token tile landed (both CTAs of a pair) and weights upcast
+    const uint32_t bar_empty = bar_full + 8 * kMaxStages;                // [kStages] slot no longer read by any MMA
+    const uint32_t bar_accfull = bar_empty + 8 * kMaxStages;             // [2]
     const uint32_t bar_accempty = bar_accfull + 8 * 2;                   // [2]
-    const uint32_t bar_drain = bar_accempty + 8 * 2;                     // [1]
+    const uint32_t bar_drain = bar_accempty + 8 * 2;                     // [2] one per issuer
     constexpr int kWordsOff = (4 * kMaxStages + 2 * kMaxTStages + 2 * 2 + 1) * 8;
     volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + kWordsOff);
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(bar_gen + kWordsOff + 4);
@@ -267,19 +276,16 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_wfull + 8 * s, 1);
             mbar_init(bar_wempty + 8 * s, 4);
         }
-        for (int s = 0; s < kAStages; ++s) {
-            mbar_init(bar_afull + 8 * s, CG);
-            mbar_init(bar_aempty + 8 * s, 1);
-        }
-        for (int t = 0; t < kTStages; ++t) {
-            mbar_init(bar_tfull + 8 * t, 4 * CG);
-            mbar_init(bar_tempty + 8 * t, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, CG + 4 * CG);                    // token producer(s) + the four warps of one transform group per CTA
+            mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(bar_accfull + 8 * a, 1);
+            mbar_init(bar_accfull + 8 * a, kIssuers);
             mbar_init(bar_accempty + 8 * a, kEpilogueWarps * CG);
         }
         mbar_init(bar_drain, 1);
+        mbar_init(bar_drain + 8, 1);
         *abort_flag = 0;
         *last_flag = 0;
         fence_mbar_init();
@@ -308,86 +314,120 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (warp == kProducerWarp || warp == kWProducerWarp) {
         // ------------------------------------------------------------------ TMA producers (one lane each): token tiles / weight bytes
-        if (lane == 0) {
-            const bool weights = warp == kWProducerWarp;
-            const uint32_t n_stages = weights ? kWStages : kAStages;
-            const uint32_t bar_free = weights ? bar_wempty : bar_aempty;
-            uint32_t it = 0;
-            bool ok = true;
-            const bool stat = p.stats != nullptr && blockIdx.x == 0;
-            StatTimer tt(stat), tw(stat);
-            long long st_total = 0, st_wait = 0;
-            tt.start();
-            for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
-                const Unit w = decode_unit<TN, CG>(p, u);
-                for (int i = 0; i < w.kb_count; ++i, ++it) {
-                    const uint32_t s = it % n_stages;
-                    const uint32_t ph = (it / n_stages) & 1u;
-                    tw.start();
-                    const bool free_ok = mbar_wait(bar_free + 8 * s, ph ^ 1u, abort_flag);
-                    tw.stop(st_wait);
-                    if (!free_ok) {
-                        give_up<CG>(p, abort_flag, kRoleProducer, (weights ? 0x100 : 0) | s);
-                        ok = false;
-                        break;
-                    }
-                    const int kb = w.kb_begin + i;
-                    if (weights) {
-                        mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
-                        tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, (w.n0 + static_cast<int>(rank) * kBW) * 2, kb * kKSteps);
-                    } else if constexpr (!kPair) {
-                        mbar_arrive_expect_tx(bar_afull + 8 * s, C::kAStageBytes);
+        // One copy instruction per ring slot, issued by lane 0.  The loop itself is run by the whole warp in lockstep, which
+        // measured about a quarter less time per k-block than a loop run by lane 0 alone.  Ring slot and parity are running
+        // values (no division) and the role is a compile-time parameter: at narrow tiles a producer's time per k-block is
+        // close to the kernel's.
+        {
+            auto produce = [&](auto weights_tag) {
+                constexpr bool kWeights = decltype(weights_tag)::value;
+                constexpr uint32_t n_stages = kWeights ? kWStages : kStages;
+                const uint32_t bar_free = kWeights ? bar_wempty : bar_empty;
+                uint32_t s = 0, ph = 0, it = 0;
+                bool ok = true;
+                const bool stat = p.stats != nullptr && blockIdx.x == 0;
+                StatTimer tt(stat), tw(stat);
+                long long st_total = 0, st_wait = 0;
+                const int n_coord = static_cast<int>(rank) * kBW * 2;                 // weight map counts 8-byte units: 2 per n
+                const int tok_off = kPair ? static_cast<int>(rank) * C::kTokLoad : 0;
+                tt.start();
+                for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
+                    const Unit w = decode_unit<TN, CG>(p, u);
+                    int kb = w.kb_begin;
+                    for (int i = 0; i < w.kb_count; ++i, ++kb, ++it) {
+                        tw.start();
+                        const bool free_ok = mbar_wait_warp(bar_free + 8 * s, ph ^ 1u, abort_flag, lane);
+                        tw.stop(st_wait);
+                        if (!free_ok) {
+                            if (lane == 0) give_up<CG>(p, abort_flag, kRoleProducer, (kWeights ? 0x100 : 0) | s);
+                            ok = false;
+                            break;
+                        }
+                        if (lane != 0) {
+                            // nothing to issue
+                        } else if constexpr (kWeights) {
+                            mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
+                            tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, w.n0 * 2 + n_coord, kb * kKSteps);
+                        } else {
+                            const uint32_t bar = kPair ? mapa_u32(bar_full + 8 * s, 0) : bar_full + 8 * s;
+                            const uint32_t dst = smem_a + s * C::kAStageBytes;
+                            if constexpr (!kPair)
+                                mbar_arrive_expect_tx(bar, C::kAStageBytes);
+                            else
+                                mbar_arrive_expect_tx_cluster(bar, C::kAStageBytes);
+                            if (p.a3d) {
+                                if constexpr (!kPair)
+                                    tma_load_3d(dst, &tmap_a, bar, 0, w.tok0, kb * kSubTiles);
+                                else
+                                    tma_load_3d_pair(dst, &tmap_a, bar, 0, w.tok0 + tok_off, kb * kSubTiles);
+                            } else {
 #pragma unroll
-                        for (int sub = 0; sub < kSubTiles; ++sub)
-                            tma_load_2d(smem_a + s * C::kAStageBytes + sub * C::kASubBytes, &tmap_a, bar_afull + 8 * s, kb * kBK + sub * kSubK,
-                                        w.tok0);
-                    } else {
-                        const uint32_t leader_bar = mapa_u32(bar_afull + 8 * s, 0);
-                        mbar_arrive_expect_tx_cluster(leader_bar, C::kAStageBytes);
-#pragma unroll
-                        for (int sub = 0; sub < kSubTiles; ++sub)
-                            tma_load_2d_pair(smem_a + s * C::kAStageBytes + sub * C::kASubBytes, &tmap_a, leader_bar, kb * kBK + sub * kSubK,
-                                             w.tok0 + static_cast<int>(rank) * C::kTokLoad);
-                    }
-                }
-            }
-            tt.stop(st_total);
-            if (stat) {
-                p.stats[weights ? 2 : 0] = st_total;
-                p.stats[weights ? 3 : 1] = st_wait;
-            }
-            if (!ok) {
-                // Let this CTA's own copies land before shared memory goes away: a bounded wait on the weight barriers armed
-                // most recently, and a short fixed pause for the token loads (their barrier may live in the pair's other CTA).
-                if (weights) {
-                    const uint32_t back = it < n_stages ? it : n_stages;
-                    for (uint32_t j = 1; j <= back; ++j) {
-                        const uint32_t jt = it - j;
-                        const uint64_t t0 = globaltimer_ns();
-                        while (!mbar_try_wait(bar_wfull + 8 * (jt % n_stages), (jt / n_stages) & 1u) && globaltimer_ns() - t0 < 1000000ull) {
+                                for (int sub = 0; sub < kSubTiles; ++sub) {
+                                    if constexpr (!kPair)
+                                        tma_load_2d(dst + sub * C::kASubBytes, &tmap_a, bar, kb * kBK + sub * kSubK, w.tok0);
+                                    else
+                                        tma_load_2d_pair(dst + sub * C::kASubBytes, &tmap_a, bar, kb * kBK + sub * kSubK, w.tok0 + tok_off);
+                                }
+                            }
+                        }
+                        if (++s == n_stages) {
+                            s = 0;
+                            ph ^= 1u;
                         }
                     }
                 }
-                const uint64_t t1 = globaltimer_ns();
-                while (globaltimer_ns() - t1 < 20000ull) {
+                tt.stop(st_total);
+                if (stat && lane == 0) {
+                    p.stats[kWeights ? 2 : 0] = st_total;
+                    p.stats[kWeights ? 3 : 1] = st_wait;
                 }
-            }
+                if (!ok && lane == 0) {
+                    // Let this CTA's own copies land before shared memory goes away: a bounded wait on the weight barriers armed
+                    // most recently, and a short fixed pause for the token loads (their barrier may live in the pair's other CTA).
+                    if constexpr (kWeights) {
+                        const uint32_t back = it < n_stages ? it : n_stages;
+                        for (uint32_t j = 1; j <= back; ++j) {
+                            const uint32_t jt = it - j;
+                            const uint64_t t0 = globaltimer_ns();
+                            while (!mbar_try_wait(bar_wfull + 8 * (jt % n_stages), (jt / n_stages) & 1u) && globaltimer_ns() - t0 < 1000000ull) {
+                            }
+                        }
+                    }
+                    const uint64_t t1 = globaltimer_ns();
+                    while (globaltimer_ns() - t1 < 20000ull) {
+                    }
+                }
+            };
+            if (warp == kWProducerWarp)
+                produce(std::true_type{});
+            else
+                produce(std::false_type{});
         }
-        // Lanes 1..31 wait here, at a warp-level convergence point, until lane 0 is done.  Without it they run ahead to the
-        // block/cluster barrier of the teardown and sit there polling for the whole kernel, which slows every working warp.
         __syncwarp();
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer (leader CTA, one lane)
+    } else if (warp == kMmaWarp || (kIssuers == 2 && warp == kMma2Warp)) {
+        // ------------------------------------------------------------------ MMA issuers (leader CTA, one lane per issuing warp)
         if (rank == 0 && lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16(kBW * CG, TN);
-            uint32_t it = 0, ui = 0;
+            const uint32_t issuer = warp == kMmaWarp ? 0u : 1u;
+            // One lane runs this loop (a loop that the whole warp runs in lockstep, with lane 0 issuing, measured slower: its
+            // waits cost more).  It is written for instruction count: for tiles narrower than 256 tokens the tensor pipe
+            // finishes a k-block sooner than one thread can issue its eight MMAs plus bookkeeping.  The ring cursor advances
+            // incrementally; per k-block there is one barrier probe and one commit.  With two issuers, issuer j takes the
+            // k-blocks i of a tile with i % 2 == j and accumulates them in accumulator j of the tile's buffer.
+            uint32_t ui = 0, kblocks = 0;
+            uint32_t s = 0, ph = 0;                                               // operand ring slot of the next k-block and its phase parity
+            bool peeked = false;                                                  // this issuer's next slot was already seen full by its last probe
             bool ok = true;
-            const bool stat = p.stats != nullptr && blockIdx.x == 0;
+            const bool stat = p.stats != nullptr && blockIdx.x == 0 && issuer == 0;
             StatTimer tt(stat), tw(stat);
-            long long st_total = 0, st_acc = 0, st_tok = 0, st_wgt = 0;
-            long long st_issue = 0;
-            bool peek_tok = false, peek_wgt = false;
-            long long st_tok_head = 0, st_wgt_head = 0, st_tok_events = 0, st_wgt_events = 0, st_tok_max = 0, st_wgt_max = 0;
+            long long st_total = 0, st_acc = 0, st_ops = 0, st_events = 0;
+            const uint64_t desc0 = umma_desc_kmajor_sw128(smem_a);
+            auto advance = [&](uint32_t& slot, uint32_t& parity) {
+                if (++slot == kStages) {
+                    slot = 0;
+                    parity ^= 1u;
+                }
+            };
             tt.start();
             for (int u = cluster_id; ok && u < p.num_units; u += num_clusters, ++ui) {
                 const Unit w = decode_unit<TN, CG>(p, u);
@@ -401,65 +441,53 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * TN;
-                for (int i = 0; i < w.kb_count; ++i, ++it) {
-                    const uint32_t s = it % kAStages;
-                    const uint32_t ph = (it / kAStages) & 1u;
-                    const uint32_t t = it % kTStages;
-                    const uint32_t tph = (it / kTStages) & 1u;
-                    // `peek_*` were probed (non-blocking) before the previous k-block's MMAs were issued, so the barrier
-                    // latency overlapped with that issue; only a phase that was still pending then is waited for here.
-                    if (!peek_tok) {
+                const uint32_t d_tmem = tmem_base + (a * kIssuers + issuer) * TN;
+                uint32_t accumulate = 0;                                          // this issuer's first MMA of a tile overwrites its accumulator
+                for (int i = 0; i < w.kb_count; ++i) {
+                    if (kIssuers == 2 && (static_cast<uint32_t>(i) & 1u) != issuer) {
+                        advance(s, ph);
+                        continue;
+                    }
+                    if (!peeked) {
                         tw.start();
-                        const bool tok_ok = mbar_wait(bar_afull + 8 * s, ph, abort_flag);
-                        tw.stop(st_tok);
-                        ++st_tok_events;
-                        if (!tok_ok) {
+                        const bool full_ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                        tw.stop(st_ops);
+                        ++st_events;
+                        if (!full_ok) {
                             give_up<CG>(p, abort_flag, kRoleMma, 0x200 | s);
                             ok = false;
                             break;
                         }
                     }
-                    if (!peek_wgt) {
-                        tw.start();
-                        const bool wgt_ok = mbar_wait(bar_tfull + 8 * t, tph, abort_flag);
-                        tw.stop(st_wgt);
-                        ++st_wgt_events;
-                        if (!wgt_ok) {
-                            give_up<CG>(p, abort_flag, kRoleMma, 0x300 | t);
-                            ok = false;
-                            break;
-                        }
-                    }
-                    {
-                        const uint32_t itn = it + 1;
-                        peek_tok = mbar_test_wait(bar_afull + 8 * (itn % kAStages), (itn / kAStages) & 1u);
-                        peek_wgt = mbar_test_wait(bar_tfull + 8 * (itn % kTStages), (itn / kTStages) & 1u);
-                    }
+                    // Probe this issuer's next slot now (non-blocking): the barrier's latency overlaps with the issue below, and
+                    // only a phase that is still pending then is waited for at the top of that k-block.  Across a tile boundary
+                    // the distance to the next own k-block varies, so nothing is probed there.
+                    uint32_t sn = s, phn = ph;
+#pragma unroll
+                    for (int j = 0; j < kIssuers; ++j) advance(sn, phn);
+                    peeked = (i + kIssuers < w.kb_count) && mbar_test_wait(bar_full + 8 * sn, phn);
                     tc_fence_after();
-                    long long t_issue = 0;
-                    if (stat) t_issue = clock64();
-                    const uint32_t a_tmem = tmem_wring + t * kTColsPerStage;
+                    const uint32_t a_tmem = tmem_wring + s * kTColsPerStage;
+                    const uint64_t b_stage = desc0 + static_cast<uint64_t>(s * (C::kAStageBytes >> 4));
 #pragma unroll
                     for (int sub = 0; sub < kSubTiles; ++sub) {
-                        const uint64_t b_desc = umma_desc_kmajor_sw128(smem_a + s * C::kAStageBytes + sub * C::kASubBytes);
 #pragma unroll
                         for (int ks = 0; ks < kSubK / 16; ++ks) {
                             // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
-                            umma_f16_ts<CG>(d_tmem, a_tmem + (sub * (kSubK / 16) + ks) * 8, b_desc + static_cast<uint64_t>(ks * 2), idesc,
-                                            (i | sub | ks) != 0 ? 1u : 0u);
+                            umma_f16_ts<CG>(d_tmem, a_tmem + (sub * (kSubK / 16) + ks) * 8,
+                                            b_stage + static_cast<uint64_t>(sub * (C::kASubBytes >> 4) + ks * 2), idesc, (sub | ks) != 0 ? 1u : accumulate);
                         }
                     }
-                    if constexpr (!kPair) {
-                        umma_commit_1cta(bar_aempty + 8 * s);
-                        umma_commit_1cta(bar_tempty + 8 * t);
-                    } else {
-                        umma_commit_pair(bar_aempty + 8 * s, 0x3);
-                        umma_commit_pair(bar_tempty + 8 * t, 0x3);
-                    }
-                    if (stat) st_issue += clock64() - t_issue;
+                    if constexpr (!kPair)
+                        umma_commit_1cta(bar_empty + 8 * s);
+                    else
+                        umma_commit_pair(bar_empty + 8 * s, 0x3);
+                    accumulate = 1u;
+                    advance(s, ph);
+                    ++kblocks;
                 }
                 if (!ok) break;
+                // every issuer commits (also one without a k-block in this tile): the barrier expects kIssuers arrivals
                 if constexpr (!kPair)
                     umma_commit_1cta(bar_accfull + 8 * a);
                 else
@@ -469,33 +497,29 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (stat) {
                 p.stats[4] = st_total;
                 p.stats[5] = st_acc;
-                p.stats[6] = st_tok;
-                p.stats[7] = st_wgt;
-                p.stats[16] = st_tok_head;      // token waits during the first kStages k-blocks of a tile
-                p.stats[17] = st_wgt_head;
-                p.stats[18] = st_tok_events;    // waits longer than 200 cycles
-                p.stats[19] = st_wgt_events;
-                p.stats[20] = st_tok_max;
-                p.stats[21] = st_wgt_max;
-                p.stats[22] = it;               // k-blocks issued
-                p.stats[23] = st_issue;         // cycles between the waits and the end of the commits (4 MMAs + 2 commits)
+                p.stats[6] = st_ops;            // waits for a full operand slot (token tile + upcast weights) that the probe had not seen
+                p.stats[7] = 0;
+                p.stats[18] = st_events;        // how many such waits
+                p.stats[22] = kblocks;          // k-blocks issued by issuer 0
             }
             // Nothing of this CTA pair may be torn down while an MMA is still reading it.
-            umma_commit_1cta(bar_drain);
+            umma_commit_1cta(bar_drain + 8 * issuer);
             {
                 const uint64_t t0 = globaltimer_ns();
-                while (!mbar_try_wait(bar_drain, 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
+                while (!mbar_try_wait(bar_drain + 8 * issuer, 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
                 }
             }
         }
-        __syncwarp();   // as for the producers: the idle lanes wait for the issuing lane here, not at the teardown barrier
+        __syncwarp();   // the idle lanes wait for the issuing lane here, not at the teardown barrier
     } else if (warp >= kFirstTransformWarp) {
         // ------------------------------------------------------------------ e5m2 -> fp16 into TMEM
         const int q = warp & 3;
         const int g = (warp - kFirstTransformWarp) >> 2;
         const uint32_t w_lane_off = static_cast<uint32_t>(q * 32 + lane) * 16u;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
-        uint32_t it = 0;
+        // Running ring positions of the next k-block (weight-byte ring, operand ring) and whose turn it is; no division in the loop.
+        uint32_t ws = 0, wph = 0, os = 0, oph = 0;
+        int turn = 0;
         bool ok = true;
         const bool stat = p.stats != nullptr && blockIdx.x == 0 && warp == kFirstTransformWarp;
         StatTimer tt(stat), tw(stat);
@@ -503,17 +527,24 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tt.start();
         for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
             const Unit w = decode_unit<TN, CG>(p, u);
-            for (int i = 0; i < w.kb_count; ++i, ++it) {
-                if (static_cast<int>(it % TG) != g) continue;
-                const uint32_t s = it % kWStages;
-                const uint32_t ph = (it / kWStages) & 1u;
-                const uint32_t t = it % kTStages;
-                const uint32_t tph = (it / kTStages) & 1u;
+            for (int i = 0; i < w.kb_count; ++i) {
+                const uint32_t s = ws, ph = wph, t = os, tph = oph;
+                const bool mine = turn == g;
+                if (++ws == kWStages) {
+                    ws = 0;
+                    wph ^= 1u;
+                }
+                if (++os == kStages) {
+                    os = 0;
+                    oph ^= 1u;
+                }
+                if (++turn == TG) turn = 0;
+                if (!mine) continue;
                 tw.start();
                 bool got = mbar_wait_warp(bar_wfull + 8 * s, ph, abort_flag, lane);
                 tw.stop(st_bytes);
                 tw.start();
-                got = got && mbar_wait_warp(bar_tempty + 8 * t, tph ^ 1u, abort_flag, lane);
+                got = got && mbar_wait_warp(bar_empty + 8 * t, tph ^ 1u, abort_flag, lane);
                 tw.stop(st_tmem);
                 if (!got) {
                     if (lane == 0) give_up<CG>(p, abort_flag, kRoleTransform, (q << 8) | s);
@@ -548,9 +579,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (lane == 0) {
                     mbar_arrive(bar_wempty + 8 * s);
                     if constexpr (!kPair)
-                        mbar_arrive(bar_tfull + 8 * t);
+                        mbar_arrive(bar_full + 8 * t);
                     else
-                        mbar_arrive_cluster(mapa_u32(bar_tfull + 8 * t, 0));
+                        mbar_arrive_cluster(mapa_u32(bar_full + 8 * t, 0));
                 }
             }
         }
@@ -603,7 +634,23 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const int n = w.n0 + col;
             const bool n_ok = n < p.N;
             const uint16_t bias_bits = (has_bias && n_ok) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + n) : uint16_t(0);
-            const uint32_t src = tmem_base + t_lane + a * TN;
+            const uint32_t src = tmem_base + t_lane + a * (kIssuers * TN);
+            // With two issuers the tile's sum is split over two accumulators (even / odd k-blocks); a tile of one k-block has
+            // nothing in the second.
+            const bool two_sums = kIssuers == 2 && w.kb_count >= 2;
+            // 16 accumulator columns starting at column c0 -> registers (fp32 bit patterns), both partial sums added.
+            auto load_sum16 = [&](int c0, uint32_t (&v)[16]) {
+                tmem_ld_32x32b_x16(src + c0, v);
+                if (two_sums) {
+                    uint32_t v2[16];
+                    tmem_ld_32x32b_x16(src + TN + c0, v2);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+                } else {
+                    tc_wait_ld();
+                }
+            };
             const int valid = p.M - w.tok0 < TN ? p.M - w.tok0 : TN;              // token columns of this tile that exist
             // The accumulator goes back to the MMA warp as soon as this warp's last TMEM load of the tile has landed.
             bool released = false;
@@ -659,6 +706,25 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                             tma_store_commit();
                         }
                     };
+                    if constexpr (kIssuers == 2) {
+                        // Narrow tiles (two partial sums): 16 columns at a time, loads not overlapped with the conversion; the
+                        // whole epilogue of such a tile is short against the weight stream it follows.
+#pragma unroll 1
+                        for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
+                            const bool last = c0 + 2 * kOutRows >= valid;
+                            block_begin();
+#pragma unroll
+                            for (int h = 0; h < kOutRows; h += 16) {
+                                uint32_t v[16];
+                                load_sum16(c0 + h, v);
+                                if (last && h + 16 >= kOutRows) release_acc();
+                                stage16(v, out_buf + h * (kBW * 2));
+                            }
+                            block_end(c0);
+                        }
+                        release_acc();
+                        return;
+                    }
                     uint32_t va[16], vb[16];
                     if (first < valid) tmem_ld_32x32b_x16(src + first, va);
 #pragma unroll 1
@@ -721,8 +787,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll 1
                     for (int c0 = grp * 16; c0 < valid; c0 += 32) {
                         uint32_t v[16];
-                        tmem_ld_32x32b_x16(src + c0, v);
-                        tc_wait_ld();
+                        load_sum16(c0, v);
                         if (c0 + 32 >= valid) release_acc();
                         if (n_ok) {
 #pragma unroll
@@ -741,8 +806,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll 1
                     for (int c0 = grp * 16; c0 < valid; c0 += 32) {
                         uint32_t v[16];
-                        tmem_ld_32x32b_x16(src + c0, v);
-                        tc_wait_ld();
+                        load_sum16(c0, v);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) __stcg(part + (c0 + j) * kTileCols + col, __uint_as_float(v[j]));
                     }
@@ -837,15 +901,18 @@ static EncodeTiledFn encode_tiled_fn() {
 // small-M kernel runs.  The key holds everything the encoding depends on, so a changed pointer or shape is a miss.
 struct TmapKey {
     const void* ptr;
-    uint64_t d0, d1, stride;
-    uint32_t b0, b1;
+    uint64_t d0, d1, d2, stride, stride2;
+    uint32_t b0, b1, b2;
     int kind, device;
     bool operator==(const TmapKey& o) const {
-        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 && kind == o.kind && device == o.device;
+        return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && stride == o.stride && stride2 == o.stride2 && b0 == o.b0 && b1 == o.b1 &&
+               b2 == o.b2 && kind == o.kind && device == o.device;
     }
 };
+// d2 == 0: a 2-D map (d0 x d1, row pitch stride_bytes); otherwise 3-D with a third dimension of pitch stride2_bytes.
 static CUresult cached_tmap(EncodeTiledFn encode, CUtensorMap* out, int kind, CUtensorMapDataType dtype, const void* ptr, uint64_t d0, uint64_t d1,
-                            uint64_t stride_bytes, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz, CUtensorMapL2promotion promo) {
+                            uint64_t stride_bytes, uint32_t b0, uint32_t b1, CUtensorMapSwizzle swz, CUtensorMapL2promotion promo, uint64_t d2 = 0,
+                            uint64_t stride2_bytes = 0, uint32_t b2 = 0) {
     constexpr int kSlots = 64;
     static std::mutex mu;
     static TmapKey keys[kSlots];
@@ -853,7 +920,7 @@ static CUresult cached_tmap(EncodeTiledFn encode, CUtensorMap* out, int kind, CU
     static bool used[kSlots];
     int dev = 0;
     cudaGetDevice(&dev);
-    const TmapKey key{ptr, d0, d1, stride_bytes, b0, b1, kind, dev};
+    const TmapKey key{ptr, d0, d1, d2, stride_bytes, stride2_bytes, b0, b1, b2, kind, dev};
     const size_t h = (reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull + d0 * 31 + d1 * 17 + b1 * 7 + kind;
     const int slot = static_cast<int>((h >> 20) % kSlots);
     {
@@ -863,11 +930,11 @@ static CUresult cached_tmap(EncodeTiledFn encode, CUtensorMap* out, int kind, CU
             return CUDA_SUCCESS;
         }
     }
-    const cuuint64_t dims[2] = {d0, d1};
-    const cuuint64_t strides[1] = {stride_bytes};
-    const cuuint32_t box[2] = {b0, b1};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(out, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, promo,
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {stride_bytes, stride2_bytes};
+    const cuuint32_t box[3] = {b0, b1, b2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(out, dtype, d2 == 0 ? 2 : 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, promo,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS) {
         std::lock_guard<std::mutex> lock(mu);
@@ -986,7 +1053,7 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-    cfg.blockDim = dim3(32 * (kEpilogueWarps + 4 * TG + 3), 1, 1);
+    cfg.blockDim = dim3(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1069,11 +1136,18 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
     }
+    const bool a3d = K % kSubK == 0;
     {
         // A as (K, M) fp16; a box is one sub-tile, 64 k x (tokens per CTA), 128-byte swizzle; rows beyond M and k beyond K read as zero.
-        const CUresult r = cached_tmap(encode, &tmap_a, 1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
-                                       static_cast<uint64_t>(K) * 2, kSubK, static_cast<uint32_t>(pl.tn / pl.cg), CU_TENSOR_MAP_SWIZZLE_128B,
-                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        // When K is a multiple of 64 the same memory is described as (64 k, M, K/64) instead, so that one copy of a
+        // (64, tokens, 2) box fetches both sub-tiles of a k-block: the producer thread pays per instruction, not per byte.
+        // A k-block past the end of K reads as zero in either form (it lies outside the tensor, never in the next row).
+        const CUresult r = a3d ? cached_tmap(encode, &tmap_a, 3, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, kSubK, static_cast<uint64_t>(M),
+                                             static_cast<uint64_t>(K) * 2, kSubK, static_cast<uint32_t>(pl.tn / pl.cg), CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, static_cast<uint64_t>(K / kSubK), kSubK * 2, kSubTiles)
+                               : cached_tmap(encode, &tmap_a, 1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                                             static_cast<uint64_t>(K) * 2, kSubK, static_cast<uint32_t>(pl.tn / pl.cg), CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with CUresult %d", static_cast<int>(r));
     }
     if (tma_store) {
@@ -1088,6 +1162,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     }
 
     MmParams p{};
+    p.a3d = a3d ? 1 : 0;
     p.tma_store = tma_store ? 1 : 0;
     p.n_dst = 1 + n_extra;
     p.scale = scale;

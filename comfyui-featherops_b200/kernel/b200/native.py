@@ -213,6 +213,7 @@ def read_stats(device):
     torch.cuda.synchronize(device)
     v = status_word_for(device)[2:66].view(torch.int64).cpu().tolist()
     return {
+        "raw": v,
         "producer": {"total": v[0], "wait_stage_free": v[1]},
         "w_producer": {"total": v[2], "wait_stage_free": v[3]},
         "mma": {"total": v[4], "wait_acc_free": v[5], "wait_tokens": v[6], "wait_weights": v[7]},

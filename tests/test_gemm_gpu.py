@@ -174,11 +174,16 @@ def test_split_k_launches_of_different_tile_counts_share_a_workspace(native, cud
 
 
 def test_tile_variants_agree_bitwise(native, cuda_dev):
-    """Without split-K every variant adds the k-blocks of an output element in the same order."""
+    """Without split-K, variants with the same number of MMA issuers add the k-blocks of an output element in the same
+    order: tiles of 192 or 256 tokens in one chain, narrower tiles as (even k-blocks) + (odd k-blocks).  CTA pairs, the
+    number of transform groups and the tile width inside a class change nothing, and neither does a repeat."""
     a, bq, s, b = _synthetic(300, 512, 1536, "bf16", seed=9)
-    outs = [_run(native, cuda_dev, a, bq, s, b, "bf16", v) for v in ((256, 1, 1, 2, 0), (128, 1, 1, 1, 0), (64, 1, 1, 2, 0), (256, 2, 1, 2, 0))]
-    for o in outs[1:]:
-        assert np.array_equal(o, outs[0])
+    one_issuer = [_run(native, cuda_dev, a, bq, s, b, "bf16", v) for v in ((256, 1, 1, 2, 0), (256, 2, 1, 2, 0), (192, 1, 1, 1, 0), (256, 1, 1, 2, 0))]
+    two_issuers = [_run(native, cuda_dev, a, bq, s, b, "bf16", v) for v in ((128, 1, 1, 1, 0), (64, 1, 1, 2, 0), (128, 2, 1, 2, 0), (16, 1, 1, 2, 0), (128, 1, 1, 1, 0))]
+    for outs in (one_issuer, two_issuers):
+        for o in outs[1:]:
+            assert np.array_equal(o, outs[0])
+    assert_gemm_close(two_issuers[0], fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
 
 
 def test_empty_and_edge_shapes(hip_kernel, native, cuda_dev):
