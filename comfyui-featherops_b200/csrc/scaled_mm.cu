@@ -975,33 +975,44 @@ static bool valid_tn(int tn) { return tn == 16 || tn == 32 || tn == 64 || tn == 
 static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant* v, size_t ws_avail, bool ws_known, int sms, Plan* out) {
     Plan pl{};
     pl.total_kb = static_cast<int>((K + kBK - 1) / kBK);
+    const int sm_total = sms > 0 ? sms : 148;
     int tn = v ? v->tokens_tile : 0;
-    if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    if (!valid_tn(tn)) return false;
     int cg = v ? v->cta_pair : 0;
-    // CTA pairs halve the token-tile traffic per SM (large M) and the MMAs issued per weight byte (small M)
-    if (cg == 0) cg = (N >= 2 * kBW) ? 2 : 1;
-    if (cg != 1 && cg != 2) return false;
+    if (cg != 0 && cg != 1 && cg != 2) return false;
+    // CTA pairs halve the token-tile traffic per SM; up to 64 tokens that traffic is small and single CTAs measured faster.
+    const int cg_auto = (N >= 2 * kBW && M > 64) ? 2 : 1;
+    if (tn == 0) {
+        tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        // One 256-token tile per column block leaves most SMs idle when N is small: two 128-token tiles instead.
+        if (tn == 256 && M <= 256) {
+            const int c = cg ? cg : cg_auto;
+            if ((N + kBW * c - 1) / (kBW * c) < sm_total / c / 2) tn = 128;
+        }
+    }
+    if (!valid_tn(tn)) return false;
+    if (cg == 0) cg = cg_auto;
     pl.tn = tn;
     pl.cg = cg;
-    pl.tg = v ? v->transform_groups : 0;
-    if (pl.tg == 0) pl.tg = 2;
-    if (pl.tg != 1 && pl.tg != 2) return false;
     pl.tiles_n = static_cast<int>((N + kBW * cg - 1) / (kBW * cg));
     pl.tiles_t = static_cast<int>((M + tn - 1) / tn);
     const long long tiles = static_cast<long long>(pl.tiles_n) * pl.tiles_t;
     if (tiles <= 0 || tiles > 0x3FFFFFFF) return false;
-    const int clusters = (sms > 0 ? sms : 148) / cg;
+    const int clusters = sm_total / cg;
+    pl.tg = v ? v->transform_groups : 0;
+    // Two transform groups keep a narrow tile's weight stream fed; a long run of 256-token tiles is bound by the tensor
+    // pipe and the power limit, where the four extra warps only cost (measured 2% under sustained load).
+    if (pl.tg == 0) pl.tg = (tn == 256 && tiles >= 2 * clusters) ? 1 : 2;
+    if (pl.tg != 1 && pl.tg != 2) return false;
     int splits = v ? v->split_k : 0;
     if (splits == 0) {
         splits = 1;
         if (tiles < 2 * clusters && pl.total_kb >= 4) {
-            // Pick the K split that minimises (rounds of work units over the clusters) x (cycles per unit).  A stage costs its
-            // eight MMAs (an MMA has a floor of ~94 cycles whatever its width); a split unit also parks an fp32 partial tile
-            // and one unit per tile reads them all back, which grows with the tokens tile (measured: splitting 128-token
-            // tiles costs more than it balances).
-            const long long stage_cycles = tn * 4 > 750 ? tn * 4 : 750;
-            const long long split_cycles = 1500 + 48LL * tn;
+            // Pick the K split that minimises (rounds of work units over the clusters) x (cycles per unit).  Measured on
+            // B200: a k-block costs about 870 cycles for tiles up to 128 tokens (issue-bound) and 1150 for 256; a split
+            // unit also parks an fp32 partial tile and one unit per tile reads them all back, about 1000 + 180 cycles per
+            // token row of the tile (6 us at 64 tokens, 11 us at 128: 256-token tiles are never worth splitting).
+            const long long stage_cycles = tn > 128 ? 1150 : 870;
+            const long long split_cycles = 1000 + 180LL * tn;
             long long best = -1;
             for (int sp = 1; sp <= pl.total_kb / 2 && sp <= 32; ++sp) {
                 const long long rounds = (tiles * sp + clusters - 1) / clusters;
@@ -1013,7 +1024,7 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
                 }
             }
         }
-        const size_t per_split = static_cast<size_t>(tiles) * tn * kBW * cg * sizeof(float);
+    const size_t per_split = static_cast<size_t>(tiles) * tn * kBW * cg * sizeof(float);
         const size_t counters = kCounterBytes;
         if (static_cast<size_t>(tiles) * cg * sizeof(int) > kCounterBytes) splits = 1;
         if (ws_known && splits > 1 && counters + per_split * splits > ws_avail) {
@@ -1104,7 +1115,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     for (int d = 0; d < n_extra; ++d)
         if (extra_dst == nullptr || extra_dst[d] == nullptr || (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15u) != 0)
             return set_error(FEATHER_ERR_BAD_ARGUMENT, "every output buffer must be non-null and 16-byte aligned");
-    if ((which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 32)) && n_extra == 0)
+    if ((which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 16)) && n_extra == 0)
         return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, sms, stream);
     if (which == FEATHER_KERNEL_STREAM) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer");
     Plan pl;
@@ -1325,6 +1336,6 @@ extern "C" int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t 
     out->split_k = pl.splits;
     out->transform_groups = pl.tg;
     out->max_ctas = 0;
-    out->kernel = M <= 32 ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
+    out->kernel = M <= 16 ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
     return FEATHER_OK;
 }

@@ -58,8 +58,8 @@ enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
  *   split_k     : number of K slices reduced through the fp32 workspace (1 = none)
  *   transform_groups : groups of four warps that upcast e5m2 weight stages (1 or 2)
  *   max_ctas    : cap on the persistent grid (0 = number of SMs)
- *   kernel      : 0 = choose from the shape; 1 = the tensor-memory (tcgen05) kernel; 2 = the register-streaming kernel for
- *                 M <= 32 tokens (bandwidth-bound shapes; needs no workspace, ignores the other fields)
+ *   kernel      : 0 = choose from the shape (streaming up to 16 tokens); 1 = the tensor-memory (tcgen05) kernel; 2 = the
+ *                 register-streaming kernel, at most 32 tokens (needs no workspace, ignores the other fields)
  */
 enum { FEATHER_KERNEL_AUTO = 0, FEATHER_KERNEL_TMEM = 1, FEATHER_KERNEL_STREAM = 2 };
 typedef struct feather_mm_variant {

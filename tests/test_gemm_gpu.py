@@ -133,14 +133,18 @@ STREAM_CASES = [
 
 @pytest.mark.parametrize("M,N,K,out_dtype,bias", STREAM_CASES)
 def test_streaming_kernel_against_oracle(native, cuda_dev, M, N, K, out_dtype, bias):
-    """The register-streaming kernel for M <= 32 (forced, and as the library's own choice)."""
+    """The register-streaming kernel (at most 32 tokens), forced, and as the library's own choice up to 16 tokens."""
     a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 11 + N + K, bias=bias)
     ref = fo.scaled_mm(a, bq, s, b, out_dtype, product="fp32")
     forced = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_STREAM))
     assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}")
     auto = _run(native, cuda_dev, a, bq, s, b, out_dtype, None)
-    assert np.array_equal(auto, forced)
-    assert native.choose_variant(M, N, K).kernel == native.KERNEL_STREAM
+    if M <= 16:     # the library's own choice up to 16 tokens; above, the tensor-memory kernel measured faster
+        assert np.array_equal(auto, forced)
+        assert native.choose_variant(M, N, K).kernel == native.KERNEL_STREAM
+    else:
+        assert_gemm_close(auto, ref, out_dtype, fo, f"auto {(M, N, K)}")
+        assert native.choose_variant(M, N, K).kernel == native.KERNEL_TMEM
     tmem = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_TMEM))
     assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}")
 
