@@ -251,6 +251,22 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
+// Fragment load: 16 lanes x 16 columns.  Thread t receives, for each group g of 8 columns, v[4g], v[4g+1] = lane t/4,
+// columns 8g + 2(t%4), +1 and v[4g+2], v[4g+3] = lane t/4 + 8, the same columns: the accumulator fragment of an m16n8
+// MMA, which is also what stmatrix consumes.  The address's lane is the first of the 16 (a multiple of 16 inside the warp's quarter).
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Four 8x8 matrices of 16-bit elements, transposed on the way: register i of thread t holds M_i[2(t%4)][t/4] (low half) and
+// M_i[2(t%4)+1][t/4] (high half); row r of matrix i goes to the 16 bytes at the address thread 8i + r supplies.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+
 // Load 32 consecutive 32-bit columns for this warp's 32 lanes (no wait: pair with tc_wait_ld()).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(

@@ -81,8 +81,11 @@ struct Cfg {
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kTStages * kTColsPerStage);   // the ring may use fewer (kAStages) slots
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kOutRows = TN < 32 ? TN : 32;                   // token rows per output staging buffer
-    static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [rows][128 n] 16-bit
-    static constexpr int kOutBytes = 2 * kOutBufBytes;                   // double buffered
+    static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [2 tiles][rows][64 n] 16-bit
+    // Staging buffers per epilogue group.  Two (a block is staged while TMA still reads the previous one) measured no
+    // faster at 256-token tiles than one: the 16 KB come out of the weight-byte ring, which then runs a stage short.
+    static constexpr int kOutBufs = 1;
+    static constexpr int kOutBytes = 2 * kOutBufs * kOutBufBytes;
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
     // One operand ring for the MMA warp: slot i holds a token tile in shared memory and the matching upcast weights in
     // tensor memory, so the single issuing thread waits on one barrier and commits to one barrier per k-block (its
@@ -205,25 +208,6 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
     __half2 v = __floats2half2_rn(r0, r1);
     if (has_bias) v = __hadd2(v, *reinterpret_cast<const __half2*>(&bias2));
     return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-// Eight packed pairs at once with the dtype and bias decisions made at compile time: inside the unrolled loop there is no
-// branch, so the eight multiply -> convert -> add chains overlap instead of running one after the other.
-template <bool kBf16, bool kBias>
-__device__ __forceinline__ void convert8(const uint32_t (&v)[16], uint32_t (&h)[8], float scale, uint32_t bias2) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float r0 = __uint_as_float(v[2 * j]) * scale, r1 = __uint_as_float(v[2 * j + 1]) * scale;
-        if constexpr (kBf16) {
-            __nv_bfloat162 x = __floats2bfloat162_rn(r0, r1);
-            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __nv_bfloat162*>(&bias2));
-            h[j] = *reinterpret_cast<const uint32_t*>(&x);
-        } else {
-            __half2 x = __floats2half2_rn(r0, r1);
-            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __half2*>(&bias2));
-            h[j] = *reinterpret_cast<const uint32_t*>(&x);
-        }
-    }
 }
 
 template <int TN, int CG, int TG>
@@ -606,8 +590,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         constexpr int kTileCols = kBW * CG;
         constexpr int kOutRows = C::kOutRows;
         const bool staged = p.tma_store != 0 && p.splits == 1;
-        const uint32_t out_buf = smem_out + grp * C::kOutBufBytes;
+        const uint32_t out_base = smem_out + grp * (C::kOutBufs * C::kOutBufBytes);
         uint32_t ui = 0;
+        uint32_t out_flip = 0;                                             // which of the group's staging buffers the next block uses
         // A warp whose wait ran out stays in the loop as a bystander (alive = false): it touches no tensor
         // memory but still joins every named barrier, so the other epilogue warps are never left waiting.
         bool alive = true;
@@ -670,97 +655,127 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
             if (staged) {
                 // Staged path: each group of four warps fills its shared-memory buffer with kOutRows token rows of the
-                // CTA's 128 output columns and one thread hands the buffer to TMA.  The loop body is free of run-time
-                // switches (output type and bias are compile-time tags, chosen once per tile).
-                const bool odd = (lane & 1) != 0;
-                const uint32_t pick = odd ? 0x3276u : 0x5410u;
-                const uint32_t bias2 = static_cast<uint32_t>(bias_bits) * 0x00010001u;
-                const uint32_t lane_off = (col_local & ~1) * 2 + (odd ? kBW * 2 : 0);
+                // CTA's 128 output columns and one thread hands the buffer to TMA.  The accumulator is read as MMA fragments
+                // (thread t: TMEM lanes = output columns t/4 + 8i, token pairs 2(t%4), +1), each pair is scaled, converted
+                // and packed into one word, and stmatrix transposes 8 token rows x 32 columns per instruction into the
+                // buffer, which is two [rows][64 columns] tiles in the 128-byte swizzle the output tensor map declares
+                // (row r keeps its 16-byte chunk c at chunk c ^ (r % 8), so the eight rows of a matrix hit distinct banks).
+                // No shuffles and no sub-word stores; output type and bias are compile-time tags, chosen once per tile.
                 const int first = grp * kOutRows;                                  // this group's blocks: first, first + 2*kOutRows, ...
                 const int store_x = w.n0 + static_cast<int>(rank) * kBW;
+                const uint32_t frag = src;                                         // lanes q*32 .. +15; +16 lanes for the upper half
+                const uint32_t frag_hi = src + (16u << 16);
+                // this thread's four output columns (one per matrix) and their bias, duplicated into both halves of a word
+                uint32_t bias2[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int nn = w.n0 + static_cast<int>(rank) * kBW + q * 32 + 8 * i + (lane >> 2);
+                    const uint32_t bb = (has_bias && nn < p.N) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + nn) : 0u;
+                    bias2[i] = bb * 0x00010001u;
+                }
+                // thread t supplies the address of row t % 8 of matrix t / 8
+                const uint32_t st_lane = (q >> 1) * (kOutRows * 128) + (lane & 7) * 128 +
+                                         (((static_cast<uint32_t>(q & 1) * 4 + (lane >> 3)) ^ (lane & 7)) << 4);
                 auto drain = [&](auto bf16_tag, auto bias_tag) {
                     constexpr bool kBf16 = decltype(bf16_tag)::value;
                     constexpr bool kBias = decltype(bias_tag)::value;
-                    // 16 accumulator columns (token rows of this tile) held in registers -> staging buffer.  Lanes 2i and
-                    // 2i+1 hold neighbouring output columns; each converts token pairs of its own column into packed words,
-                    // swaps them with its neighbour and picks, with one byte permute, the 32-bit word {column 2i, column
-                    // 2i+1} of one token row (even lane: the pair's first token, odd lane: the second).  Sub-word
-                    // shared-memory stores, and one fused convert-exchange-store loop, were both several times slower.
-                    auto stage16 = [&](const uint32_t (&v)[16], uint32_t buf_rows) {
-                        uint32_t h[8];
-                        convert8<kBf16, kBias>(v, h, scale, bias2);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) h[j] = __byte_perm(h[j], __shfl_xor_sync(0xffffffffu, h[j], 1), pick);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) asm volatile("st.shared.u32 [%0], %1;" ::"r"(buf_rows + lane_off + 2 * j * (kBW * 2)), "r"(h[j]));
+                    auto pack = [&](uint32_t x0, uint32_t x1, uint32_t b2) -> uint32_t {
+                        const float r0 = __uint_as_float(x0) * scale, r1 = __uint_as_float(x1) * scale;
+                        if constexpr (kBf16) {
+                            __nv_bfloat162 x = __floats2bfloat162_rn(r0, r1);
+                            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __nv_bfloat162*>(&b2));
+                            return *reinterpret_cast<const uint32_t*>(&x);
+                        } else {
+                            __half2 x = __floats2half2_rn(r0, r1);
+                            if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __half2*>(&b2));
+                            return *reinterpret_cast<const uint32_t*>(&x);
+                        }
                     };
+                    // 16 token rows (accumulator columns c .. c+15) -> rows row0 .. row0+15 of the staging buffer
+                    auto store16 = [&](const uint32_t (&lo)[8], const uint32_t (&hi)[8], uint32_t buf, int row0) {
+#pragma unroll
+                        for (int g = 0; g < 2; ++g)
+                            stmatrix_x4_trans(buf + st_lane + (row0 + 8 * g) * 128, pack(lo[4 * g], lo[4 * g + 1], bias2[0]), pack(lo[4 * g + 2], lo[4 * g + 3], bias2[1]),
+                                              pack(hi[4 * g], hi[4 * g + 1], bias2[2]), pack(hi[4 * g + 2], hi[4 * g + 3], bias2[3]));
+                    };
+                    auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+                        tmem_ld_16x256b_x2(frag + c, lo);
+                        tmem_ld_16x256b_x2(frag_hi + c, hi);
+                    };
+                    auto add_second = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {   // the odd k-blocks' partial sum
+                        uint32_t lo2[8], hi2[8];
+                        tmem_ld_16x256b_x2(frag + TN + c, lo2);
+                        tmem_ld_16x256b_x2(frag_hi + TN + c, hi2);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(lo2[j]));
+                            hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(hi2[j]));
+                        }
+                    };
+                    // One bulk group per block: with two buffers the group before the last may still be reading.
                     auto block_begin = [&]() {
-                        if (group_leader) tma_store_wait_read<0>();              // the previous store of this group has read the buffer
+                        if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                     };
-                    auto block_end = [&](int c0) {
+                    auto block_end = [&](uint32_t buf, int c0) {
                         fence_proxy_async_smem();
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                         if (group_leader) {
-                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&tmap_c.m[d], out_buf, store_x, w.tok0 + c0);
+                            for (int d = 0; d < p.n_dst; ++d) {
+                                tma_store_2d(&tmap_c.m[d], buf, store_x, w.tok0 + c0);
+                                if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, w.tok0 + c0);
+                            }
                             tma_store_commit();
                         }
                     };
+                    constexpr int kPasses = kOutRows / 16;                         // 16 token rows per pass
                     if constexpr (kIssuers == 2) {
-                        // Narrow tiles (two partial sums): 16 columns at a time, loads not overlapped with the conversion; the
-                        // whole epilogue of such a tile is short against the weight stream it follows.
+                        // Narrow tiles (two partial sums): loads are not overlapped with the conversion; the whole epilogue
+                        // of such a tile is short against the weight stream it follows.
 #pragma unroll 1
                         for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
                             const bool last = c0 + 2 * kOutRows >= valid;
                             block_begin();
 #pragma unroll
-                            for (int h = 0; h < kOutRows; h += 16) {
-                                uint32_t v[16];
-                                load_sum16(c0 + h, v);
-                                if (last && h + 16 >= kOutRows) release_acc();
-                                stage16(v, out_buf + h * (kBW * 2));
+                            for (int ps = 0; ps < kPasses; ++ps) {
+                                uint32_t lo[8], hi[8];
+                                load16(c0 + 16 * ps, lo, hi);
+                                if (two_sums)
+                                    add_second(c0 + 16 * ps, lo, hi);
+                                else
+                                    tc_wait_ld();
+                                if (last && ps == kPasses - 1) release_acc();
+                                store16(lo, hi, out_base, 16 * ps);
                             }
-                            block_end(c0);
+                            block_end(out_base, c0);
                         }
                         release_acc();
-                        return;
-                    }
-                    uint32_t va[16], vb[16];
-                    if (first < valid) tmem_ld_32x32b_x16(src + first, va);
+                    } else {
+                        // Wide tiles: the fragment loads of the next 16 token rows are in flight while the current 16 are
+                        // converted and stored.
+                        uint32_t lo[8], hi[8], lo_n[8], hi_n[8];
+                        if (first < valid) load16(first, lo, hi);
 #pragma unroll 1
-                    for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
-                        const int next = c0 + 2 * kOutRows;
-                        if constexpr (kOutRows == 16) {
+                        for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
+                            const int next = c0 + 2 * kOutRows;
+                            static_assert(kIssuers == 2 || kPasses == 2, "wide tiles stage 32 rows per block");
+                            const uint32_t buf = out_base + out_flip * C::kOutBufBytes;
                             tc_wait_ld();
-                            if (next < valid) {
-                                tmem_ld_32x32b_x16(src + next, vb);               // vb doubles as the next block's buffer
-                            } else {
-                                release_acc();
-                            }
+                            load16(c0 + 16, lo_n, hi_n);
                             block_begin();
-                            stage16(va, out_buf);
-                            block_end(c0);
-                            if (next < valid) {
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) va[j] = vb[j];
-                            }
-                        } else {
-                            // the TMEM load of the next 16 columns is in flight while the current 16 are converted and staged
+                            store16(lo, hi, buf, 0);
                             tc_wait_ld();
-                            tmem_ld_32x32b_x16(src + c0 + 16, vb);
-                            block_begin();
-                            stage16(va, out_buf);
-                            tc_wait_ld();
-                            if (next < valid) {
-                                tmem_ld_32x32b_x16(src + next, va);
-                            } else {
+                            if (next < valid)
+                                load16(next, lo, hi);
+                            else
                                 release_acc();
-                            }
-                            stage16(vb, out_buf + 16 * kBW * 2);
-                            block_end(c0);
+                            store16(lo_n, hi_n, buf, 16);
+                            block_end(buf, c0);
+                            out_flip ^= (C::kOutBufs - 1);
                         }
+                        release_acc();                                             // a group without any block in this tile
                     }
-                    release_acc();                                                 // a group without any block in this tile
                 };
                 tw.start();
                 if (alive) {
@@ -1162,12 +1177,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed with CUresult %d", static_cast<int>(r));
     }
     if (tma_store) {
-        // C as (N, M) 16-bit with row pitch ldc; a box is 128 n x (up to 32) token rows, clipped at N and M
+        // C as (N, M) 16-bit with row pitch ldc; a box is 64 n x (up to 32) token rows in the 128-byte swizzle, clipped at N and M
         for (int d = 0; d <= n_extra; ++d) {
             void* const dst = d == 0 ? c : extra_dst[d - 1];
             const CUresult r = cached_tmap(encode, &tmap_c.m[d], 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, static_cast<uint64_t>(N),
-                                           static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, kBW, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32),
-                                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+                                           static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, 64, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32),
+                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
             if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
         }
     }

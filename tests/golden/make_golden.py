@@ -1,7 +1,7 @@
 """Generates tests/golden/golden.npz by running the REFERENCE's own code on the seeded inputs of cases.py.
 
-Needs a checkout of woct0rdho/ComfyUI-FeatherOps (default /root/reference, override with FEATHER_REFERENCE_DIR) and torch on
-CPU.  The reference modules are imported by file path (never copied): kernel/naive.py as is, comfy_feather/quant.py under the
+Needs a checkout of woct0rdho/ComfyUI-FeatherOps (default: a directory named `reference` beside this repository, override
+with FEATHER_REFERENCE_DIR) and torch on CPU.  The reference modules are imported by file path (never copied): kernel/naive.py as is, comfy_feather/quant.py under the
 test double of the `comfy` package in tests/fake_comfy.  While generating, it also asserts that the numpy oracle
 (oracle/feather_oracle.py) reproduces every reference output, which is what pins the oracle.
 
@@ -24,7 +24,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests", "fake_comfy"))
 from oracle import feather_oracle as fo  # noqa: E402
 from tests.golden import cases  # noqa: E402
 
-REF = os.environ.get("FEATHER_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("FEATHER_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def load_by_path(name, path):
