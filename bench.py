@@ -279,9 +279,9 @@ def run_ours(args):
     achieved = local_flops / (gemm_ms * 1e-3) / 1e12
     timed_seconds = ms * 1e-3
     peak = peaks["tflops_sustained"] if timed_seconds >= 2.0 else peaks["tflops"]
-    # DRAM bytes per launch of the dominant kernel from the ncu capture in profiles/ (279.5 MB at M = 4096, N = 13824,
+    # DRAM bytes per launch of the dominant kernel from the ncu capture in profiles/ (278.9 MB at M = 4096, N = 13824,
     # K = 5120), scaled by the token count for the ffn-up launch of this run; null for other workloads.
-    traffic = 279.5e6 * (M / 4096.0) if (not args.shape and args.workload == "wan" and world == 1) else None
+    traffic = 278.9e6 * (M / 4096.0) if (not args.shape and args.workload == "wan" and world == 1) else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
         "traffic_note": "ncu dram read+write of the (5120,13824) launch at M=4096, scaled by M/4096; algorithmic bytes of that launch: 1.31e9",

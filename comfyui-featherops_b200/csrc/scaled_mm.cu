@@ -114,6 +114,7 @@ struct MmParams {
     long long ldc;
     int out_bf16;
     int a3d;       // 1: the token tensor map is the 3-D form (64 k, M, K/64): one copy per k-block
+    int c3d;       // 1: the output tensor maps are the 3-D form (64 n, M, N/64): one store per staged block and destination
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
     int n_dst;     // number of output buffers every tile is stored to (1, or one per GPU of a column-sharded linear)
     int splits;
@@ -723,8 +724,12 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                         if (group_leader) {
                             for (int d = 0; d < p.n_dst; ++d) {
-                                tma_store_2d(&tmap_c.m[d], buf, store_x, w.tok0 + c0);
-                                if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, w.tok0 + c0);
+                                if (p.c3d) {
+                                    tma_store_3d(&tmap_c.m[d], buf, 0, w.tok0 + c0, store_x >> 6);   // both 64-column tiles at once
+                                } else {
+                                    tma_store_2d(&tmap_c.m[d], buf, store_x, w.tok0 + c0);
+                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, w.tok0 + c0);
+                                }
                             }
                             tma_store_commit();
                         }
@@ -1163,6 +1168,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
     }
     const bool a3d = K % kSubK == 0;
+    const bool c3d = N % 64 == 0;
     {
         // A as (K, M) fp16; a box is one sub-tile, 64 k x (tokens per CTA), 128-byte swizzle; rows beyond M and k beyond K read as zero.
         // When K is a multiple of 64 the same memory is described as (64 k, M, K/64) instead, so that one copy of a
@@ -1180,15 +1186,22 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         // C as (N, M) 16-bit with row pitch ldc; a box is 64 n x (up to 32) token rows in the 128-byte swizzle, clipped at N and M
         for (int d = 0; d <= n_extra; ++d) {
             void* const dst = d == 0 ? c : extra_dst[d - 1];
-            const CUresult r = cached_tmap(encode, &tmap_c.m[d], 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, static_cast<uint64_t>(N),
-                                           static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, 64, static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32),
-                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+            // When N is a multiple of 64 the same memory is described as (64 n, M, N/64), so one store of a (64, rows, 2) box
+            // writes both staged tiles: the storing thread pays per instruction (and per destination GPU).
+            const uint32_t rows = static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32);
+            const CUresult r = c3d ? cached_tmap(encode, &tmap_c.m[d], 4, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, 64, static_cast<uint64_t>(M),
+                                                 static_cast<uint64_t>(ldc) * 2, 64, rows, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                                 static_cast<uint64_t>(N / 64), 128, 2)
+                                   : cached_tmap(encode, &tmap_c.m[d], 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, static_cast<uint64_t>(N),
+                                                 static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, 64, rows, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_NONE);
             if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
         }
     }
 
     MmParams p{};
     p.a3d = a3d ? 1 : 0;
+    p.c3d = c3d ? 1 : 0;
     p.tma_store = tma_store ? 1 : 0;
     p.n_dst = 1 + n_extra;
     p.scale = scale;
