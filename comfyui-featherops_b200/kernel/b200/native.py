@@ -138,6 +138,58 @@ def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+# ------------------------------------------------------------------------------------------------
+# Hot-path helpers.  A small-M GEMM runs 15-25 us on the GPU; the general-purpose route (a device context manager, a
+# Stream object, seven c_void_p objects per call) measured 19 us of host time per call, so the GEMM entry points use
+# the raw-integer forms below.
+# ------------------------------------------------------------------------------------------------
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream          # (device index) -> cudaStream_t as int
+except AttributeError:                                        # pragma: no cover - older/newer torch without the private hook
+    def _raw_stream(index):
+        return torch.cuda.current_stream(index).cuda_stream
+
+
+class _OnDevice:
+    """`with _OnDevice(index):` makes `index` the current CUDA device for the C call, and costs nothing when it already is."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, index):
+        self.index = index
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+_scratch_ptrs = {}
+
+
+def _scratch_ptrs_for(dev):
+    """(workspace pointer, workspace bytes, status-word pointer) of a device as plain integers, cached."""
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    got = _scratch_ptrs.get(index)
+    if got is None:
+        ws = workspace_for(dev)
+        st = status_word_for(dev)
+        got = (index, ws.data_ptr(), ws.numel(), st.data_ptr())
+        _scratch_ptrs[index] = got
+    return got
+
+
+def _addr(t):
+    return t.data_ptr() if t is not None else None
+
+
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
@@ -253,16 +305,16 @@ def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
     dev = _require_cuda(a, b_prepacked, scale, bias, c)
     M, K = a.shape
     N = b_prepacked.shape[1] if n_cols is None else n_cols
-    ws = workspace_for(dev)
-    st = status_word_for(dev)
-    with torch.cuda.device(dev):
+    index, ws_ptr, ws_bytes, st_ptr = _scratch_ptrs_for(dev)
+    with _OnDevice(index):
         status = lib.feather_scaled_mm_ex(
-            _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c),
+            a.data_ptr(), b_prepacked.data_ptr(), _addr(scale), _addr(bias), c.data_ptr(),
             M, N, K, c.stride(0), _OUT_CODE[c.dtype],
             ctypes.byref(variant) if variant is not None else None,
-            _ptr(ws), ws.numel(), _ptr(st), _stream_ptr(dev),
+            ws_ptr, ws_bytes, st_ptr, _raw_stream(index),
         )
-    _check(status, "feather_scaled_mm_ex")
+    if status != FEATHER_OK:
+        _check(status, "feather_scaled_mm_ex")
     return c
 
 

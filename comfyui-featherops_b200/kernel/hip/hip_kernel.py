@@ -36,47 +36,86 @@ def _check(cond, msg):
 
 
 def _validate(a, b_prepacked, scale, bias, c, b_dtype):
-    """Argument checks of the reference op (hip_kernel.cu:648-730), minus tile divisibility of M and N."""
-    _check(a.is_cuda, "a must be a CUDA tensor")
-    _check(b_prepacked.is_cuda, "b_prepacked must be a CUDA tensor")
-    _check(c.is_cuda, "c must be a CUDA tensor")
-    _check(b_prepacked.device == a.device, "b_prepacked must be on the same device as a")
-    _check(c.device == a.device, "c must be on the same device as a")
-    _check(a.dtype == torch.float16, "a must be float16")
-    _check(c.dtype in (torch.float16, torch.bfloat16), "c must be float16 or bfloat16")
-    _check(b_dtype in (0, 1), "b_dtype must be 0 (fp8e4m3) or 1 (fp8e5m2)")
-    _check(b_dtype == 1, "fp8e4m3 weights are not supported by the sm_100a kernel; b_dtype must be 1 (fp8e5m2)")
-    _check(b_prepacked.dtype == torch.float8_e5m2, "b_prepacked must be float8_e5m2 when b_dtype=1")
-    _check(a.dim() == 2, "a must be 2D")
-    _check(b_prepacked.dim() == 3, "b_prepacked must be 3D (K/16, N, 16)")
-    _check(c.dim() == 2, "c must be 2D")
+    """Argument checks of the reference op (hip_kernel.cu:648-730), minus tile divisibility of M and N.
+
+    Written as plain `if` statements so that a message is only formatted when its check fails: this runs on every call and
+    a small-M GEMM takes less time on the GPU than thirty formatted strings take on the host."""
+    if not (a.is_cuda):
+        raise RuntimeError("a must be a CUDA tensor")
+    if not (b_prepacked.is_cuda):
+        raise RuntimeError("b_prepacked must be a CUDA tensor")
+    if not (c.is_cuda):
+        raise RuntimeError("c must be a CUDA tensor")
+    if not (b_prepacked.device == a.device):
+        raise RuntimeError("b_prepacked must be on the same device as a")
+    if not (c.device == a.device):
+        raise RuntimeError("c must be on the same device as a")
+    if not (a.dtype == torch.float16):
+        raise RuntimeError("a must be float16")
+    if not (c.dtype in (torch.float16, torch.bfloat16)):
+        raise RuntimeError("c must be float16 or bfloat16")
+    if not (b_dtype in (0, 1)):
+        raise RuntimeError("b_dtype must be 0 (fp8e4m3) or 1 (fp8e5m2)")
+    if not (b_dtype == 1):
+        raise RuntimeError("fp8e4m3 weights are not supported by the sm_100a kernel; b_dtype must be 1 (fp8e5m2)")
+    if not (b_prepacked.dtype == torch.float8_e5m2):
+        raise RuntimeError("b_prepacked must be float8_e5m2 when b_dtype=1")
+    if not (a.dim() == 2):
+        raise RuntimeError("a must be 2D")
+    if not (b_prepacked.dim() == 3):
+        raise RuntimeError("b_prepacked must be 3D (K/16, N, 16)")
+    if not (c.dim() == 2):
+        raise RuntimeError("c must be 2D")
     M, K = a.shape
     N = b_prepacked.shape[1]
-    _check(K % 16 == 0, "K must be divisible by 16")
-    _check(b_prepacked.shape[0] == K // 16, f"b_prepacked.shape[0] must equal K/16 ({K // 16})")
-    _check(b_prepacked.shape[2] == 16, "b_prepacked.shape[2] must be 16")
-    _check(c.shape[0] == M, "c.shape[0] must equal M")
-    _check(c.shape[1] == N, "c.shape[1] must equal N")
-    _check(a.stride(0) == K or M <= 1, f"a.stride(0) must equal K ({K})")
-    _check(a.stride(1) == 1, "a.stride(1) must be 1")
-    _check(b_prepacked.stride(0) == N * 16 or K == 16, f"b_prepacked.stride(0) must equal N*16 ({N * 16})")
-    _check(b_prepacked.stride(1) == 16, "b_prepacked.stride(1) must be 16")
-    _check(b_prepacked.stride(2) == 1, "b_prepacked.stride(2) must be 1")
-    _check(c.stride(0) >= N or M <= 1, f"c.stride(0) must be at least N ({N})")
-    _check(c.stride(1) == 1, "c.stride(1) must be 1")
+    if not (K % 16 == 0):
+        raise RuntimeError("K must be divisible by 16")
+    if not (b_prepacked.shape[0] == K // 16):
+        raise RuntimeError(f"b_prepacked.shape[0] must equal K/16 ({K // 16})")
+    if not (b_prepacked.shape[2] == 16):
+        raise RuntimeError("b_prepacked.shape[2] must be 16")
+    if not (c.shape[0] == M):
+        raise RuntimeError("c.shape[0] must equal M")
+    if not (c.shape[1] == N):
+        raise RuntimeError("c.shape[1] must equal N")
+    if not (a.stride(0) == K or M <= 1):
+        raise RuntimeError(f"a.stride(0) must equal K ({K})")
+    if not (a.stride(1) == 1):
+        raise RuntimeError("a.stride(1) must be 1")
+    if not (b_prepacked.stride(0) == N * 16 or K == 16):
+        raise RuntimeError(f"b_prepacked.stride(0) must equal N*16 ({N * 16})")
+    if not (b_prepacked.stride(1) == 16):
+        raise RuntimeError("b_prepacked.stride(1) must be 16")
+    if not (b_prepacked.stride(2) == 1):
+        raise RuntimeError("b_prepacked.stride(2) must be 1")
+    if not (c.stride(0) >= N or M <= 1):
+        raise RuntimeError(f"c.stride(0) must be at least N ({N})")
+    if not (c.stride(1) == 1):
+        raise RuntimeError("c.stride(1) must be 1")
     if scale is not None:
-        _check(scale.is_cuda, "scale must be a CUDA tensor")
-        _check(scale.device == a.device, "scale must be on the same device as a")
-        _check(scale.dtype == torch.float32, "scale must be float32")
-        _check(scale.numel() == 1, "scale must have one element")
+        if not (scale.is_cuda):
+            raise RuntimeError("scale must be a CUDA tensor")
+        if not (scale.device == a.device):
+            raise RuntimeError("scale must be on the same device as a")
+        if not (scale.dtype == torch.float32):
+            raise RuntimeError("scale must be float32")
+        if not (scale.numel() == 1):
+            raise RuntimeError("scale must have one element")
     if bias is not None:
-        _check(bias.is_cuda, "bias must be a CUDA tensor")
-        _check(bias.device == a.device, "bias must be on the same device as a")
-        _check(bias.dtype == c.dtype, "bias must have the same dtype as c")
-        _check(bias.numel() == N, "bias must have N elements")
-        _check(bias.is_contiguous(), "bias must be contiguous")
-    _check(a.data_ptr() % 16 == 0, "a data pointer must be 16-byte aligned")
-    _check(b_prepacked.data_ptr() % 16 == 0, "b_prepacked data pointer must be 16-byte aligned")
+        if not (bias.is_cuda):
+            raise RuntimeError("bias must be a CUDA tensor")
+        if not (bias.device == a.device):
+            raise RuntimeError("bias must be on the same device as a")
+        if not (bias.dtype == c.dtype):
+            raise RuntimeError("bias must have the same dtype as c")
+        if not (bias.numel() == N):
+            raise RuntimeError("bias must have N elements")
+        if not (bias.is_contiguous()):
+            raise RuntimeError("bias must be contiguous")
+    if not (a.data_ptr() % 16 == 0):
+        raise RuntimeError("a data pointer must be 16-byte aligned")
+    if not (b_prepacked.data_ptr() % 16 == 0):
+        raise RuntimeError("b_prepacked data pointer must be 16-byte aligned")
 
 
 # ------------------------------------------------------------------------------------------------
