@@ -314,7 +314,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 StatTimer tt(stat), tw(stat);
                 long long st_total = 0, st_wait = 0;
                 const int n_coord = static_cast<int>(rank) * kBW * 2;                 // weight map counts 8-byte units: 2 per n
-                const int tok_off = kPair ? static_cast<int>(rank) * C::kTokLoad : 0;
+                [[maybe_unused]] const int tok_off = kPair ? static_cast<int>(rank) * C::kTokLoad : 0;   // token role of a pair only
                 tt.start();
                 for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
                     const Unit w = decode_unit<TN, CG>(p, u);
