@@ -257,6 +257,10 @@ def run_ours(args):
         ms = float(t.item())
     ms_per_step = ms / args.steps
     flops_step = sum(2.0 * M * K * N for K, N in kn_list)
+    # bytes one step touches (activations, weights, outputs of all its linears) against the 126 MB L2
+    step_mb = sum(2.0 * M * K + K * N + 2.0 * M * N for K, N in kn_list) / 1e6
+    l2_note = (f"one step touches {step_mb:.0f} MB over {len(kn_list)} linears "
+               + ("(larger than the 126 MB L2, so no launch finds its inputs cached)" if step_mb > 252 else "(not larger than twice the 126 MB L2 and no flush between launches: a probe shape, not a bench line)"))
     tflops = flops_step / (ms_per_step * 1e-3) / 1e12
 
     # per-GEMM kernel time on this rank (events on the launching stream), for the roofline line
@@ -308,7 +312,7 @@ def run_ours(args):
             "metric": "TFLOPS fp16@fp8e5m2 scaled_mm at Wan-14B shapes", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp16xfp8e5m2->fp32", "data": "synthetic",
-            "config": {"workload": desc, "out_dtype": out_dtype, "l2": "inputs larger than L2 (A and C are 335-906 MB per linear)",
+            "config": {"workload": desc, "out_dtype": out_dtype, "l2": l2_note,
                        "parallelism": "single GPU" if world == 1 else (
                            f"weights sharded by output columns over {world} GPUs; " + ("each rank's epilogue TMA-stores its blocks into every rank's output over NVLink (fused exchange)"
                                                                                       if args.exchange == "peer_store" else "NCCL all-gather of the output + relayout")),
