@@ -156,11 +156,15 @@ __global__ void scale_from_amax_kernel(const uint32_t* __restrict__ amax_bits, i
 }
 
 // ------------------------------------------------------------------------------------------------
-// quantise + prepack.  One block converts a tile of 32 weight rows (n) x 128 k and writes 8 k16-block
-// planes of 32 n x 16 bytes (512 contiguous bytes each).
+// quantise + prepack.  One block converts a tile of 32 weight rows (n) x 128 k (fp32 source) or 256 k (16-bit source) and
+// writes 8 or 16 k16-block planes of 32 n x 16 bytes (512 contiguous bytes each).
 // ------------------------------------------------------------------------------------------------
 constexpr int kQRows = 32;
-constexpr int kQK = 128;
+// k extent of a tile: 512 bytes of every source row, whatever the source type (shorter row segments cost DRAM efficiency)
+template <int kSrc>
+struct QTile {
+    static constexpr int kK = (kSrc == FEATHER_SRC_FP32) ? 128 : 256;
+};
 
 template <int kSrc>
 __global__ void __launch_bounds__(256)
@@ -168,8 +172,9 @@ quantize_prepack_kernel(const void* __restrict__ src, const float* __restrict__ 
                         uint8_t* __restrict__ dst, int N, int K) {
     using S = Src<kSrc>;
     constexpr int kPer = S::kPerVec;
-    constexpr int kVecPerRow = kQK / kPer;                 // 32 (fp32) or 16 (16-bit)
-    constexpr int kIters = kQRows * kVecPerRow / 256;      // 4 or 2
+    constexpr int kQK = QTile<kSrc>::kK;
+    constexpr int kVecPerRow = kQK / kPer;                 // 32 16-byte vectors per row segment
+    constexpr int kIters = kQRows * kVecPerRow / 256;      // 4
     __shared__ __align__(16) uint8_t tile[kQK / 16][kQRows + 1][16];   // +1 row: conflict-free 16-byte access both ways
 
     // Blocks walk the weight from its end to its start: the amax pass that ran just before read it start to end, so the
@@ -213,9 +218,11 @@ quantize_prepack_kernel(const void* __restrict__ src, const float* __restrict__ 
         }
     }
     __syncthreads();
-    {
-        const int kb = threadIdx.x / kQRows;
-        const int row = threadIdx.x % kQRows;
+#pragma unroll
+    for (int it = 0; it < (kQK / 16) * kQRows / 256; ++it) {
+        const int idx = it * 256 + threadIdx.x;
+        const int kb = idx / kQRows;
+        const int row = idx % kQRows;
         const int n = n0 + row;
         const int k = k0 + kb * 16;
         if (n < N && k < K) {
@@ -408,7 +415,8 @@ extern "C" int feather_quantize_prepack(const void* src, int src_dtype, const fl
         scale_from_amax_kernel<<<1, 1, 0, stream>>>(amax_scratch, src_dtype == FEATHER_SRC_FP16 ? 1 : 0, scale_io);
         if (int st = check_launch("scale")) return st;
     }
-    const dim3 grid(static_cast<unsigned>((K + kQK - 1) / kQK), static_cast<unsigned>((N + kQRows - 1) / kQRows));
+    const int qk = src_dtype == FEATHER_SRC_FP32 ? QTile<FEATHER_SRC_FP32>::kK : QTile<FEATHER_SRC_BF16>::kK;
+    const dim3 grid(static_cast<unsigned>((K + qk - 1) / qk), static_cast<unsigned>((N + kQRows - 1) / kQRows));
     switch (src_dtype) {
         case FEATHER_SRC_FP32:
             quantize_prepack_kernel<FEATHER_SRC_FP32><<<grid, 256, 0, stream>>>(src, premul, scale_io, dst, static_cast<int>(N), static_cast<int>(K));
