@@ -6,13 +6,14 @@
 //   out^T tile [128 weight columns n  x  TN tokens]  +=  up(W)[128 n x 16 k]  *  A^T[16 k x TN tokens]
 //
 //   producer warps  TMA: W bytes  [8 k16-blocks][128 n][16 B] (the prepacked layout, verbatim; 2 KB rows) -> smem ring
-//                   TMA: A tokens 2 x [TN rows][64 k] fp16, 128-byte swizzle                     -> smem ring
+//                   TMA: A tokens 2 x [TN rows][64 k] fp16, 128-byte swizzle (one 3-D copy per k-block) -> operand ring
 //   transform warps ld.shared 16 B (one n, 16 k) -> 8 x prmt (e5m2 -> fp16 is `byte << 8`, exact)
-//                   -> tcgen05.st into a TMEM ring (64 columns per 128-k stage); fp16 W never touches smem
-//   MMA warp        tcgen05.mma kind::f16, A from TMEM, B (tokens) from smem descriptor, D fp32 in TMEM
-//   epilogue warps  tcgen05.ld -> *scale -> RTNE to out dtype -> +bias in out dtype -> global stores
-//                   (lane = n, so a warp writes 32 consecutive n of one token row); split-K slices park
-//                   fp32 partials in a workspace and the last slice to arrive reduces them in slice order.
+//                   -> tcgen05.st into the operand ring's TMEM half (64 columns per 128-k slot); fp16 W never touches smem
+//   MMA warp(s)     tcgen05.mma kind::f16, A from TMEM, B (tokens) from smem descriptor, D fp32 in TMEM; tiles of at most
+//                   128 tokens have two issuing threads (even / odd k-blocks, one accumulator each)
+//   epilogue warps  tcgen05.ld (MMA fragment shape) -> *scale -> RTNE to out dtype -> +bias in out dtype -> stmatrix into a
+//                   swizzled staging tile -> TMA store; split-K slices park fp32 partials in a workspace and the last
+//                   slice to arrive reduces them in slice order.
 //
 // CG = 2 pairs two CTAs on one 256-n tile (tcgen05 cta_group::2): each CTA loads/transforms its own
 // 128 n and half of the tokens; barriers that the issuing CTA needs are signalled across the pair.
