@@ -404,7 +404,7 @@ def run_smallm(args, native, dev):
         del w
         copies = [bq] + [bq.clone() for _ in range(3)]
         s = s.reshape(1)
-        for M in (1, 16, 128):
+        for M in (1, 8, 16, 64, 128):
             a = torch.randn((M, K), generator=g, device=dev).to(torch.float16)
             c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
             variant = native.make_variant(*[int(x) for x in args.variant.split(",")]) if args.variant else None
