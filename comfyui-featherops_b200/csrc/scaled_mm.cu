@@ -725,7 +725,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         fence_proxy_async_smem();
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                         if (group_leader) {
-                            for (int d = 0; d < p.n_dst; ++d) {
+                            // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
+                            for (int d = 0; d < (store_x < p.N ? p.n_dst : 0); ++d) {
                                 if (p.c3d) {
                                     tma_store_3d(&tmap_c.m[d], buf, 0, w.tok0 + c0, store_x >> 6);   // both 64-column tiles at once
                                 } else {
