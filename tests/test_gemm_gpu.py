@@ -257,6 +257,27 @@ def test_column_shard_writes_in_place(native, cuda_dev):
     assert np.array_equal(from_torch(C), full)
 
 
+@pytest.mark.parametrize("M,N,K,g", [(700, 13824, 1024, 8), (700, 5120, 1024, 8), (300, 13824, 512, 4)])
+def test_ragged_column_shards_reproduce_the_full_output(native, cuda_dev, M, N, K, g):
+    """The column shards of 4 and 8 ranks (1728, 640, 3456 columns: not multiples of the 256-column pair tile, so the last
+    pair stores a clipped block and its second CTA may have nothing to store), written in place through the fused-exchange
+    entry point with one destination: bitwise the unsharded output."""
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device=cuda_dev, dtype=torch.float16)
+    B = torch.randint(0, 0x7B, (K // 16, N, 16), dtype=torch.uint8, device=cuda_dev).view(torch.float8_e5m2)
+    S = torch.full((1,), 1e-2, device=cuda_dev)
+    bias = torch.randn(N, device=cuda_dev).to(torch.bfloat16)
+    full = torch.empty(M, N, device=cuda_dev, dtype=torch.bfloat16)
+    native.scaled_mm_into(A, B, S, bias, full)
+    sharded = torch.full((M, N), float("nan"), device=cuda_dev, dtype=torch.bfloat16)
+    n = N // g
+    for r in range(g):
+        Br = B[:, r * n:(r + 1) * n, :].contiguous()
+        native.scaled_mm_multi_into(A, Br, S, bias[r * n:(r + 1) * n].contiguous(), [sharded[:, r * n:(r + 1) * n]])
+    native.check_device_status(cuda_dev)
+    assert torch.equal(full.view(torch.int16), sharded.view(torch.int16))
+
+
 def test_multi_destination_epilogue_on_one_gpu(native, cuda_dev):
     """The fused-exchange launch with all destinations on one GPU: every buffer receives the block, bitwise equal to the
     ordinary launch; column ranges of a wider buffer are written in place and nothing else is touched."""
