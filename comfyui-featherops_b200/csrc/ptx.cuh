@@ -240,6 +240,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
                  : "memory");
 }
 
+// Pair form without multicast: one arrive on `bar` (this CTA's barrier) once the pair's MMAs issued so far have completed.
+// A kernel's tcgen05 instructions must all name the same cta_group, so the pair kernels use this form wherever the
+// single-CTA kernels use umma_commit_1cta.
+__device__ __forceinline__ void umma_commit_2cta_local(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // Store 8 consecutive 32-bit columns for this warp's 32 lanes (lane i of the warp -> TMEM lane base+i).
 __device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&v)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),

@@ -490,7 +490,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 p.stats[22] = kblocks;          // k-blocks issued by issuer 0
             }
             // Nothing of this CTA pair may be torn down while an MMA is still reading it.
-            umma_commit_1cta(bar_drain + 8 * issuer);
+            if constexpr (!kPair)
+                umma_commit_1cta(bar_drain + 8 * issuer);
+            else
+                umma_commit_2cta_local(bar_drain + 8 * issuer);
             {
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(bar_drain + 8 * issuer, 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
@@ -1110,6 +1113,15 @@ static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtens
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                    int output_dtype, int sms, cudaStream_t stream);   // small_m.cu
 
+// Bandwidth-bound end (at most 16 tokens, or on request): the register-streaming kernel, unless the caller pinned a
+// tensor-memory variant or the output goes to several buffers.  split_k = 1 only says "no workspace" (the reference-ABI
+// launcher passes it): the streaming kernel never splits K through a workspace either, so that alone pins nothing.
+static bool takes_streaming_kernel(const feather_mm_variant* variant, int64_t M, int n_extra) {
+    const int which = variant ? variant->kernel : FEATHER_KERNEL_AUTO;
+    const bool pinned = variant && (variant->tokens_tile || variant->cta_pair || variant->split_k > 1 || variant->transform_groups);
+    return (which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 16)) && n_extra == 0 && M <= 32;
+}
+
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
                           int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant, void* workspace,
                           size_t workspace_bytes, int* status_dev, cudaStream_t stream, void* const* extra_dst = nullptr, int n_extra = 0) {
@@ -1133,12 +1145,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     if (which != FEATHER_KERNEL_AUTO && which != FEATHER_KERNEL_TMEM && which != FEATHER_KERNEL_STREAM)
         return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.kernel must be 0 (auto), 1 (tensor memory) or 2 (streaming)");
     if (which == FEATHER_KERNEL_STREAM && M > 32) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel handles at most 32 tokens");
-    const bool pinned = variant && (variant->tokens_tile || variant->cta_pair || variant->split_k || variant->transform_groups);
+
     if (n_extra < 0 || n_extra > kMaxDst - 1) return set_error(FEATHER_ERR_BAD_ARGUMENT, "at most %d output buffers", kMaxDst);
     for (int d = 0; d < n_extra; ++d)
         if (extra_dst == nullptr || extra_dst[d] == nullptr || (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15u) != 0)
             return set_error(FEATHER_ERR_BAD_ARGUMENT, "every output buffer must be non-null and 16-byte aligned");
-    if ((which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 16)) && n_extra == 0)
+    if (takes_streaming_kernel(variant, M, n_extra))
         return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, sms, stream);
     if (which == FEATHER_KERNEL_STREAM) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer");
     Plan pl;
@@ -1321,32 +1333,32 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
     if (M == 0) return FEATHER_OK;
+    // The register-streaming kernel needs no scratch at all: when the library (or the caller) picks it, nothing of the
+    // built-in array is touched and the call is exactly feather_scaled_mm_ex's.
+    if (takes_streaming_kernel(variant, M, 0))
+        return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, nullptr, 0, status_dev, stream);
     const int sms = sm_count_of_current_device();
     if (sms <= 0) return set_error(FEATHER_ERR_NO_DEVICE, "no CUDA device");
+    // The same plan feather_scaled_mm_ex makes when it is handed a workspace of this size: a K split the library chose
+    // itself is shrunk to what the array holds, and only a split the caller pinned can ask for more than there is.
     Plan pl;
-    if (!make_plan(M, N, K, variant, 0, false, sms, &pl)) return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
+    if (!make_plan(M, N, K, variant, kStaticScratchBytes, true, sms, &pl)) return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
     if (pl.ws_bytes > kStaticScratchBytes)
         return set_error(FEATHER_ERR_WORKSPACE,
-                         "this shape needs %zu bytes of split-K scratch but the built-in scratch holds %zu; use feather_scaled_mm_ex with "
+                         "this variant needs %zu bytes of split-K scratch but the built-in scratch holds %zu; use feather_scaled_mm_ex with "
                          "a caller-provided workspace, or pass a variant with a smaller split_k",
                          pl.ws_bytes, kStaticScratchBytes);
     void* scratch = nullptr;
-    if (int st = static_scratch_of_current_device(&scratch)) return st;
-    feather_mm_variant fixed{};
-    fixed.tokens_tile = pl.tn;
-    fixed.cta_pair = pl.cg;
-    fixed.split_k = pl.splits;
-    fixed.transform_groups = pl.tg;
-    fixed.max_ctas = pl.max_ctas;
-    fixed.kernel = FEATHER_KERNEL_TMEM;   // this entry point exists for the variant that needs scratch
     if (pl.splits > 1) {
+        if (int st = static_scratch_of_current_device(&scratch)) return st;
         // Every call shares the array and it keeps the previous call's contents.  Only the tile counters have to start at
         // zero; partial tiles are fully written before they are read.
         const size_t counter_bytes = static_cast<size_t>(pl.tiles_n) * pl.tiles_t * pl.cg * sizeof(int);
         const cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, stream);
         if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "clearing the tile counters failed: %s", cudaGetErrorString(e));
     }
-    return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, &fixed, scratch, kStaticScratchBytes, status_dev, stream);
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, scratch, scratch ? kStaticScratchBytes : 0, status_dev,
+                          stream);
 }
 
 extern "C" size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant) {

@@ -172,17 +172,31 @@ class _OnDevice:
 
 
 _scratch_ptrs = {}
+_MAX_STREAM_WORKSPACES = 8    # per process: 64 MiB each, so side streams beyond this run unsplit instead of allocating more
 
 
-def _scratch_ptrs_for(dev):
-    """(workspace pointer, workspace bytes, status-word pointer) of a device as plain integers, cached."""
+def _scratch_ptrs_for(dev, stream):
+    """(device index, workspace pointer, workspace bytes, status-word pointer) for GEMM launches on `stream` (a raw
+    cudaStream_t as an int), cached.
+
+    Split-K launches that may overlap on the GPU need separate workspaces (tile counters and fp32 partials live there), so
+    the workspace belongs to the (device, stream) pair, not to the device: two threads or side streams doing split-K GEMMs
+    on one GPU never share one.  After _MAX_STREAM_WORKSPACES distinct streams a further stream gets no workspace, which
+    makes the library choose a variant without a K split for it (correct, a little slower at small token counts).
+    """
     index = dev.index if dev.index is not None else torch.cuda.current_device()
-    got = _scratch_ptrs.get(index)
+    key = (index, stream)
+    got = _scratch_ptrs.get(key)
     if got is None:
-        ws = workspace_for(dev)
         st = status_word_for(dev)
-        got = (index, ws.data_ptr(), ws.numel(), st.data_ptr())
-        _scratch_ptrs[index] = got
+        with _scratch_lock:
+            n_ws = sum(1 for k in _workspaces if k[1] == index)
+        if n_ws < _MAX_STREAM_WORKSPACES:
+            ws = workspace_for(dev, stream)
+            got = (index, ws.data_ptr(), ws.numel(), st.data_ptr())
+        else:
+            got = (index, None, 0, st.data_ptr())
+        _scratch_ptrs[key] = got
     return got
 
 
@@ -204,17 +218,23 @@ _status_words = {}
 _amax_words = {}
 
 
-def workspace_for(device):
-    """Zero-initialised split-K workspace of `device` (allocated on first use through torch's allocator).
+def workspace_for(device, stream=None):
+    """Zero-initialised split-K workspace for launches on `stream` of `device` (a raw cudaStream_t as an int; default: the
+    current stream), allocated on first use through torch's allocator.
 
     The kernel leaves the tile counters at the start of the workspace at zero after every launch, so one buffer
-    serves every later call on the same stream.
+    serves every later call on the same stream; launches on another stream get a buffer of their own.
     """
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if stream is None:
+        stream = _raw_stream(index)
+    key = (device.type, index, stream)
     with _scratch_lock:
         ws = _workspaces.get(key)
         if ws is None:
             ws = torch.zeros(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+            # the zero fill ran on torch's current stream; the first GEMM may be enqueued on another one
+            torch.cuda.current_stream(device).synchronize()
             _workspaces[key] = ws
         return ws
 
@@ -251,6 +271,14 @@ def check_device_status(device=None):
     value = int(st[0].item())
     if value != 0:
         st.zero_()
+        # a launch that gave up may have left split-K tile counters behind: every later split-K launch on that workspace
+        # would reduce too early or never, so put the counters of this device's workspaces back to zero
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        with _scratch_lock:
+            for key, ws in _workspaces.items():
+                if key[1] == index:
+                    ws[:65536].zero_()
+        torch.cuda.synchronize(device)
         role = (value >> 8) & 0xFF
         detail = (value >> 16) & 0xFFFF
         names = {1: "TMA producer", 2: "MMA issuer", 3: "transform warp", 4: "epilogue warp"}
@@ -305,13 +333,15 @@ def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
     dev = _require_cuda(a, b_prepacked, scale, bias, c)
     M, K = a.shape
     N = b_prepacked.shape[1] if n_cols is None else n_cols
-    index, ws_ptr, ws_bytes, st_ptr = _scratch_ptrs_for(dev)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    stream = _raw_stream(index)
+    index, ws_ptr, ws_bytes, st_ptr = _scratch_ptrs_for(dev, stream)
     with _OnDevice(index):
         status = lib.feather_scaled_mm_ex(
             a.data_ptr(), b_prepacked.data_ptr(), _addr(scale), _addr(bias), c.data_ptr(),
             M, N, K, c.stride(0), _OUT_CODE[c.dtype],
             ctypes.byref(variant) if variant is not None else None,
-            ws_ptr, ws_bytes, st_ptr, _raw_stream(index),
+            ws_ptr, ws_bytes, st_ptr, stream,
         )
     if status != FEATHER_OK:
         _check(status, "feather_scaled_mm_ex")

@@ -79,7 +79,8 @@ typedef struct feather_mm_variant {
  * order and meaning, cudaStream_t in place of hipStream_t.  The five tile integers are accepted and
  * ignored (the variant is chosen from the shape); b_dtype must be 1 (e5m2).  Returns 1 when the launch
  * was enqueued, 0 otherwise (the reference returns false for an unknown config).  This entry point
- * takes no workspace, so it never uses a split-K variant. */
+ * takes no workspace, so it never splits K through one: up to 16 tokens it runs the register-streaming kernel (which
+ * splits K inside a CTA), above that the tensor-memory kernel unsplit. */
 FEATHER_API int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
                      int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, int block_warps_m, int block_warps_n,
                      int unroll_k, int repeat_m, int repeat_n, int b_dtype, int output_dtype, feather_stream_t stream);
@@ -119,13 +120,17 @@ FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64
 
 /* For callers that cannot allocate device memory themselves - code running inside a CUDA-graph capture or a host
  * callback, plugins that are handed pointers by an allocator they do not own, or C programs that want to link the
- * library and call one function without managing a workspace.  Same arguments and results as feather_scaled_mm_ex, minus
- * the workspace: the split-K scratch is a fixed array of feather_scaled_mm_static_scratch_bytes() bytes (8 MiB) inside
- * the library's device image, so every GPU that loads the library holds those bytes until the process exits.
- *   - Shapes whose chosen variant needs more scratch than that are rejected with FEATHER_ERR_WORKSPACE (the message says
- *     how much is needed); pass a variant with a smaller split_k, or use feather_scaled_mm_ex.
- *   - The call allocates and frees nothing.  The first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call outside any stream capture.
+ * library and call one function without managing a workspace.  Same arguments and results as feather_scaled_mm_ex called
+ * with a workspace of feather_scaled_mm_static_scratch_bytes() bytes (8 MiB), minus the workspace argument: the split-K
+ * scratch is a fixed array of that size inside the library's device image, so every GPU that loads the library holds
+ * those bytes until the process exits.
+ *   - A K split the library chooses itself (variant NULL or split_k 0) is shrunk to what the array holds, exactly as
+ *     feather_scaled_mm_ex shrinks it to the caller's workspace.  Only a variant that pins a larger split_k is rejected,
+ *     with FEATHER_ERR_WORKSPACE (the message says how much is needed): pass a smaller split_k, or use feather_scaled_mm_ex.
+ *   - Up to 16 tokens the library's own choice is the register-streaming kernel, which uses no scratch; such calls (and
+ *     variant.kernel = FEATHER_KERNEL_STREAM) never touch the array.
+ *   - The call allocates and frees nothing.  The first call on each device that needs the array looks its device address
+ *     up (cudaGetSymbolAddress, with that device current) and keeps it; make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps what the previous call left there; the call clears the tile
  *     counters it is about to use on `stream` before launching.  Two calls that can overlap on the GPU (different
  *     streams, no dependency) would race on it: serialise them or use feather_scaled_mm_ex with separate workspaces.

@@ -71,9 +71,9 @@ def test_benchmark_distribution(golden, hip_kernel, native, cuda_dev, name):
     native.check_device_status(cuda_dev)
     got = from_torch(out)
     rows = golden[f"gemm/{name}/rows"]
-    assert_gemm_close(got[rows], golden[f"gemm/{name}/out_rows"], c["out_dtype"], fo, name + " vs fixture")
+    assert_gemm_close(got[rows], golden[f"gemm/{name}/out_rows"], c["out_dtype"], fo, name + " vs fixture", has_bias=c["bias"] is not None)
     ref = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp32")
-    assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle")
+    assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle", has_bias=c["bias"] is not None)
 
 
 # (M, N, K, out_dtype, (tokens_tile, cta_pair, split_k, transform_groups, max_ctas), bias, scale)
@@ -112,7 +112,7 @@ def test_variants_against_oracle(native, cuda_dev, M, N, K, out_dtype, variant, 
     a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 7 + N * 3 + K, bias=bias)
     got = _run(native, cuda_dev, a, bq, s if scale else None, b, out_dtype, variant)
     ref = fo.scaled_mm(a, bq, s if scale else None, b, out_dtype, product="fp32")
-    assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}")
+    assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}", has_bias=bias)
 
 
 STREAM_CASES = [
@@ -137,16 +137,16 @@ def test_streaming_kernel_against_oracle(native, cuda_dev, M, N, K, out_dtype, b
     a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 11 + N + K, bias=bias)
     ref = fo.scaled_mm(a, bq, s, b, out_dtype, product="fp32")
     forced = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_STREAM))
-    assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}")
+    assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}", has_bias=bias)
     auto = _run(native, cuda_dev, a, bq, s, b, out_dtype, None)
     if M <= 16:     # the library's own choice up to 16 tokens; above, the tensor-memory kernel measured faster
         assert np.array_equal(auto, forced)
         assert native.choose_variant(M, N, K).kernel == native.KERNEL_STREAM
     else:
-        assert_gemm_close(auto, ref, out_dtype, fo, f"auto {(M, N, K)}")
+        assert_gemm_close(auto, ref, out_dtype, fo, f"auto {(M, N, K)}", has_bias=bias)
         assert native.choose_variant(M, N, K).kernel == native.KERNEL_TMEM
     tmem = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_TMEM))
-    assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}")
+    assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}", has_bias=bias)
 
 
 def test_streaming_kernel_rejects_many_tokens(native, cuda_dev):
@@ -175,6 +175,32 @@ def test_split_k_launches_of_different_tile_counts_share_a_workspace(native, cud
     a, bq, s, b = _synthetic(16, 13824, 1024, "bf16", seed=32)
     got = _run(native, cuda_dev, a, bq, s, b, "bf16", (16, 1, 4, 2, 0))
     assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
+
+
+def test_split_k_on_two_streams_does_not_share_a_workspace(native, cuda_dev):
+    """Split-K launches on two streams of one device may overlap on the GPU; each stream has a workspace of its own, so
+    neither sees the other's tile counters or partial sums."""
+    shapes = [(48, 5120, 4096, (64, 1, 4, 2, 0)), (16, 13824, 2048, (16, 1, 4, 2, 0))]
+    streams = [torch.cuda.Stream(cuda_dev) for _ in shapes]
+    work = []
+    for (M, N, K, variant), st in zip(shapes, streams):
+        a, bq, s, b = _synthetic(M, N, K, "bf16", seed=M + N + K)
+        A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
+        S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+        Bi = to_torch(b, "bf16", cuda_dev)
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+        work.append((st, A, B, S, Bi, C, native.make_variant(*variant), fo.scaled_mm(a, bq, s, b, "bf16")))
+    torch.cuda.synchronize()
+    for _ in range(20):                                   # interleaved launches, nothing orders one stream after the other
+        for st, A, B, S, Bi, C, v, _ in work:
+            with torch.cuda.stream(st):
+                native.scaled_mm_into(A, B, S, Bi, C, variant=v)
+    torch.cuda.synchronize()
+    native.check_device_status(cuda_dev)
+    ws = {native.workspace_for(cuda_dev, st.cuda_stream).data_ptr() for st, *_ in work}
+    assert len(ws) == 2
+    for st, A, B, S, Bi, C, v, ref in work:
+        assert_gemm_close(from_torch(C), ref, "bf16", fo, f"stream {st.cuda_stream:#x}")
 
 
 def test_tile_variants_agree_bitwise(native, cuda_dev):
@@ -240,6 +266,14 @@ def test_reference_c_abi_signature(native, cuda_dev):
     torch.cuda.synchronize()
     assert_gemm_close(from_torch(C), fo.scaled_mm(a, bq, s, b, "fp16"), "fp16", fo)
     assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C, b_dtype=0) == 0      # e4m3 is not supported
+    # a handful of tokens through the same signature: the streaming kernel (this entry point has no workspace to split K through)
+    C8 = torch.empty((8, 256), dtype=torch.float16, device=cuda_dev)
+    assert native.launch_scaled_mm_reference_abi(A[:8].contiguous(), B, S, Bi, C8) == 1
+    torch.cuda.synchronize()
+    stream8 = torch.empty_like(C8)
+    native.scaled_mm_into(A[:8].contiguous(), B, S, Bi, stream8, variant=native.make_variant(kernel=native.KERNEL_STREAM))
+    assert torch.equal(C8, stream8)
+    assert_gemm_close(from_torch(C8), fo.scaled_mm(a[:8], bq, s, b, "fp16"), "fp16", fo)
 
 
 def test_column_shard_writes_in_place(native, cuda_dev):
@@ -315,7 +349,7 @@ def test_full_size_wan_shapes_properties(native, cuda_dev, K, N):
     native.check_device_status(cuda_dev)
     rows = np.unique(np.concatenate([np.arange(0, M, 4099), [M - 1, 255, 256, M - 257]]))
     ref = fo.scaled_mm(from_torch(A[rows]), from_torch(B), np.float32(S.item()), None, "bf16", product="fp32")
-    assert_gemm_close(from_torch(C[rows]), ref, "bf16", fo, "sampled rows")
+    assert_gemm_close(from_torch(C[rows]), ref, "bf16", fo, "sampled rows", has_bias=False)
     # linearity in powers of two is exact (no overflow at this scale)
     C2 = torch.empty_like(C)
     native.scaled_mm_into(A * 2, B, S, None, C2)
@@ -333,7 +367,7 @@ def test_small_m_sweep(native, cuda_dev, M, K, N):
     """The bandwidth-bound sweep of the benchmark, full K and N, checked in full against the oracle."""
     a, bq, s, _ = _synthetic(M, N, K, "bf16", seed=M + K, bias=False)
     got = _run(native, cuda_dev, a, bq, s, None, "bf16")
-    assert_gemm_close(got, fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"M={M}")
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"M={M}", has_bias=False)
 
 
 @pytest.mark.parametrize("K,N", [(3072, 3072), (3072, 9216), (3072, 12288), (12288, 3072)])
@@ -343,4 +377,4 @@ def test_qwen_image_shapes(native, cuda_dev, K, N):
     a, bq, s, _ = _synthetic(M, N, K, "fp16", seed=K + N, bias=False)
     got = _run(native, cuda_dev, a, bq, s, None, "fp16")
     rows = np.arange(0, M, 68)
-    assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}")
+    assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}", has_bias=False)

@@ -46,17 +46,25 @@ def test_static_scratch_entry_matches_workspace_entry_twice(native, cuda_dev):
 
 
 def test_static_scratch_entry_with_library_chosen_variant(native, cuda_dev):
-    M, N, K = 16, 5120, 2048
-    a, bq, s, bias = _case(M, N, K, seed=7)
-    A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
-    S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
-    for _ in range(2):
-        got = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_dev)
-        native.scaled_mm_static_into(A, B, S, None, got)
-        ref = torch.empty_like(got)
-        native.scaled_mm_into(A, B, S, None, ref, variant=native.make_variant(kernel=native.KERNEL_TMEM))   # same kernel family, library-chosen split
-        native.check_device_status(cuda_dev)
-        assert torch.equal(got.view(torch.int16), ref.view(torch.int16))
+    """No variant passed: the entry point makes the choice feather_scaled_mm_ex makes with an 8 MiB workspace.  Up to 16
+    tokens that is the streaming kernel (no scratch); at (128, 4096, 8192) the library's unconstrained choice is a 4-way
+    K split that needs more than the array holds, and the entry point must shrink it, not refuse."""
+    limit = native.static_scratch_bytes()
+    for M, N, K in ((16, 5120, 2048), (8, 1024, 4096), (128, 4096, 8192), (64, 5120, 5120)):
+        a, bq, s, bias = _case(M, N, K, seed=7 + M)
+        A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
+        S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+        same_choice = native.choose_variant(M, N, K, workspace_bytes=limit)
+        if M == 128:
+            assert native.workspace_bytes(M, N, K) > limit >= native.workspace_bytes(M, N, K, same_choice) > 0
+        for _ in range(2):
+            got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+            native.scaled_mm_static_into(A, B, S, None, got)
+            ref = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+            native.scaled_mm_into(A, B, S, None, ref, variant=None if M <= 16 else same_choice)
+            native.check_device_status(cuda_dev)
+            assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), (M, N, K)
+        assert_gemm_close(from_torch(got), fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"{(M, N, K)}", has_bias=False)
 
 
 def test_static_scratch_entry_rejects_oversized_requests(native, cuda_dev):
