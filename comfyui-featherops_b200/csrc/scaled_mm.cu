@@ -61,7 +61,9 @@ __host__ __device__ constexpr int pow2_at_least(int x) {
     return p;
 }
 
-template <int TN, int CG>
+// OB: staging buffers per epilogue group.  1 for an ordinary launch; 4 (a whole 256-token tile per CTA) when the blocks also go
+// to peer GPUs, so that NVLink takes its time over a tile while the tensor cores already run the next one.
+template <int TN, int CG, int OB = 1>
 struct Cfg {
     static_assert(TN == 16 || TN == 32 || TN == 64 || TN == 128 || TN == 192 || TN == 256, "tokens tile");
     static_assert(CG == 1 || CG == 2, "cta group");
@@ -84,9 +86,12 @@ struct Cfg {
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kOutRows = TN < 32 ? TN : 32;                   // token rows per output staging buffer
     static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [2 tiles][rows][64 n] 16-bit
-    // Staging buffers per epilogue group.  Two (a block is staged while TMA still reads the previous one) measured no
-    // faster at 256-token tiles than one: the 16 KB come out of the weight-byte ring, which then runs a stage short.
-    static constexpr int kOutBufs = 1;
+    // Staging buffers per epilogue group.  On one GPU two (a block is staged while TMA still reads the previous one)
+    // measured no faster at 256-token tiles than one: the 16 KB come out of the weight-byte ring, which then runs a stage
+    // short.  With peer destinations the picture changes: a tile's blocks leave at NVLink speed (3 or 7 copies of each),
+    // which takes about as long as the tile's MMAs, and with one buffer the accumulator is held until they have left.
+    static_assert(OB == 1 || (OB == 4 && TN == 256), "staging ring depth");
+    static constexpr int kOutBufs = OB;
     static constexpr int kOutBytes = 2 * kOutBufs * kOutBufBytes;
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
     // One operand ring for the MMA warp: slot i holds a token tile in shared memory and the matching upcast weights in
@@ -119,6 +124,7 @@ struct MmParams {
     int c3d;       // 1: the output tensor maps are the 3-D form (64 n, M, N/64): one store per staged block and destination
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
     int n_dst;     // number of output buffers every tile is stored to (1, or one per GPU of a column-sharded linear)
+    int scatter_rows;  // 0: every block goes to all n_dst buffers; > 0: buffer d owns the token rows [d * scatter_rows, (d + 1) * scatter_rows)
     int splits;
     int tiles_n, tiles_t, num_units, total_kb;
 };
@@ -213,11 +219,11 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int TN, int CG, int TG>
+template <int TN, int CG, int TG, int OB = 1>
 __global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ OutMaps tmap_c, const MmParams p) {
-    using C = Cfg<TN, CG>;
+    using C = Cfg<TN, CG, OB>;
     constexpr int kStages = C::kAStages;                                  // operand ring depth (token tile + upcast weights per slot)
     constexpr int kWStages = C::kWStages;
     constexpr int kAccs = C::kAccs;
@@ -598,7 +604,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const bool staged = p.tma_store != 0 && p.splits == 1;
         const uint32_t out_base = smem_out + grp * (C::kOutBufs * C::kOutBufBytes);
         uint32_t ui = 0;
-        uint32_t out_flip = 0;                                             // which of the group's staging buffers the next block uses
+        uint32_t out_flip = 0;                                             // blocks this group has staged so far (its staging ring position)
         // A warp whose wait ran out stays in the loop as a bystander (alive = false): it touches no tensor
         // memory but still joins every named barrier, so the other epilogue warps are never left waiting.
         bool alive = true;
@@ -729,12 +735,19 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
                         if (group_leader) {
                             // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
-                            for (int d = 0; d < (store_x < p.N ? p.n_dst : 0); ++d) {
+                            int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
+                            if (p.scatter_rows > 0 && d_end > 0) {
+                                // row-sharded destinations: the block goes to the one buffer that owns its token rows
+                                d_begin = row / p.scatter_rows;
+                                row -= d_begin * p.scatter_rows;
+                                d_end = d_begin + 1;
+                            }
+                            for (int d = d_begin; d < d_end; ++d) {
                                 if (p.c3d) {
-                                    tma_store_3d(&tmap_c.m[d], buf, 0, w.tok0 + c0, store_x >> 6);   // both 64-column tiles at once
+                                    tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
                                 } else {
-                                    tma_store_2d(&tmap_c.m[d], buf, store_x, w.tok0 + c0);
-                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, w.tok0 + c0);
+                                    tma_store_2d(&tmap_c.m[d], buf, store_x, row);
+                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
                                 }
                             }
                             tma_store_commit();
@@ -771,7 +784,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         for (int c0 = first; c0 < valid; c0 += 2 * kOutRows) {
                             const int next = c0 + 2 * kOutRows;
                             static_assert(kIssuers == 2 || kPasses == 2, "wide tiles stage 32 rows per block");
-                            const uint32_t buf = out_base + out_flip * C::kOutBufBytes;
+                            // The group's staging ring is used round-robin over all its blocks, across tiles.  The position is derived from
+                            // the block's place in the tile plus a count carried between tiles: a counter bumped inside this loop
+                            // made the compiler spill.
+                            const uint32_t buf = out_base + ((out_flip + static_cast<uint32_t>(c0 - first) / (2 * kOutRows)) % C::kOutBufs) * C::kOutBufBytes;
                             tc_wait_ld();
                             load16(c0 + 16, lo_n, hi_n);
                             block_begin();
@@ -783,7 +799,6 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                 release_acc();
                             store16(lo_n, hi_n, buf, 16);
                             block_end(buf, c0);
-                            out_flip ^= (C::kOutBufs - 1);
                         }
                         release_acc();                                             // a group without any block in this tile
                     }
@@ -805,7 +820,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                 }
                 tw.stop(st_emit);
-                if (first < valid) st_chunks += (valid - first + 2 * kOutRows - 1) / (2 * kOutRows);
+                if (first < valid) {
+                    const uint32_t blocks = static_cast<uint32_t>(valid - first + 2 * kOutRows - 1) / (2 * kOutRows);
+                    out_flip += blocks;
+                    st_chunks += blocks;
+                }
             } else if (p.splits == 1) {
                 // Direct path (output rows that TMA cannot address: a row pitch that is not a multiple of 16 bytes)
                 uint16_t* const c_col = c16 + static_cast<long long>(w.tok0) * p.ldc + n;
@@ -1070,11 +1089,11 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     return true;
 }
 
-template <int TN, int CG, int TG>
+template <int TN, int CG, int TG, int OB = 1>
 static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p, int grid,
                                   cudaStream_t stream) {
-    using C = Cfg<TN, CG>;
-    auto kernel = scaled_mm_kernel<TN, CG, TG>;
+    using C = Cfg<TN, CG, OB>;
+    auto kernel = scaled_mm_kernel<TN, CG, TG, OB>;
     static std::mutex mu;
     static bool configured[64];
     int dev = 0;
@@ -1104,8 +1123,12 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
 }
 
 template <int TN>
-static cudaError_t launch_tn(int cg, int tg, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p, int grid,
-                             cudaStream_t s) {
+static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p,
+                             int grid, cudaStream_t s) {
+    if constexpr (TN == 256) {
+        // pairs of 256-token tiles whose blocks also cross NVLink: a staging ring that holds a whole tile
+        if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 4>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2, 4>(tw, ta, tc, p, grid, s);
+    }
     if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
     return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
 }
@@ -1124,7 +1147,8 @@ static bool takes_streaming_kernel(const feather_mm_variant* variant, int64_t M,
 
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
                           int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant, void* workspace,
-                          size_t workspace_bytes, int* status_dev, cudaStream_t stream, void* const* extra_dst = nullptr, int n_extra = 0) {
+                          size_t workspace_bytes, int* status_dev, cudaStream_t stream, void* const* extra_dst = nullptr, int n_extra = 0,
+                          int64_t scatter_rows = 0) {
     if (a == nullptr || b == nullptr || c == nullptr) return set_error(FEATHER_ERR_BAD_ARGUMENT, "a, b_prepacked and c must not be null");
     if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
     if (K % 16 != 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "K must be divisible by 16");
@@ -1182,6 +1206,11 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(W) failed with CUresult %d", static_cast<int>(r));
     }
+    // Row-sharded destinations (scatter_rows > 0): buffer d receives the blocks of token rows [d * scatter_rows, (d + 1) * scatter_rows)
+    // and is described as a tensor of scatter_rows rows, so a block must not straddle two owners.
+    if (scatter_rows < 0 || (scatter_rows > 0 && (scatter_rows % 32 != 0 || scatter_rows * (1 + n_extra) < M || scatter_rows * n_extra >= M || !tma_store)))
+        return set_error(FEATHER_ERR_BAD_ARGUMENT,
+                         "row-sharded output: rows per buffer must be a positive multiple of 32, the buffers must cover M, rows must be 16-byte aligned");
     const bool a3d = K % kSubK == 0;
     const bool c3d = N % 64 == 0;
     {
@@ -1204,11 +1233,13 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
             // When N is a multiple of 64 the same memory is described as (64 n, M, N/64), so one store of a (64, rows, 2) box
             // writes both staged tiles: the storing thread pays per instruction (and per destination GPU).
             const uint32_t rows = static_cast<uint32_t>(pl.tn < 32 ? pl.tn : 32);
-            const CUresult r = c3d ? cached_tmap(encode, &tmap_c.m[d], 4, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, 64, static_cast<uint64_t>(M),
+            // a row-sharded destination holds its owner's token rows only (the last one possibly fewer): rows beyond are clipped
+            const int64_t c_rows = scatter_rows > 0 ? (M - d * scatter_rows < scatter_rows ? M - d * scatter_rows : scatter_rows) : M;
+            const CUresult r = c3d ? cached_tmap(encode, &tmap_c.m[d], 4, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, 64, static_cast<uint64_t>(c_rows),
                                                  static_cast<uint64_t>(ldc) * 2, 64, rows, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                                  static_cast<uint64_t>(N / 64), 128, 2)
                                    : cached_tmap(encode, &tmap_c.m[d], 2, CU_TENSOR_MAP_DATA_TYPE_UINT16, dst, static_cast<uint64_t>(N),
-                                                 static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 2, 64, rows, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 static_cast<uint64_t>(c_rows), static_cast<uint64_t>(ldc) * 2, 64, rows, CU_TENSOR_MAP_SWIZZLE_128B,
                                                  CU_TENSOR_MAP_L2_PROMOTION_NONE);
             if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", static_cast<int>(r));
         }
@@ -1219,6 +1250,11 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.c3d = c3d ? 1 : 0;
     p.tma_store = tma_store ? 1 : 0;
     p.n_dst = 1 + n_extra;
+    p.scatter_rows = static_cast<int>(scatter_rows);
+    // variant.staging: 0 = a tile-deep staging ring whenever blocks go to more than one buffer, 1 = never, 2 = always
+    const int staging_mode = variant ? variant->staging : 0;
+    if (staging_mode < 0 || staging_mode > 2) return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.staging must be 0 (auto), 1 (one buffer) or 2 (a whole tile)");
+    const bool deep_staging = tma_store && (staging_mode == 2 || (staging_mode == 0 && n_extra > 0));
     p.scale = scale;
     p.bias = bias;
     p.c = c;
@@ -1248,12 +1284,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
 
     cudaError_t e = cudaErrorInvalidValue;
     switch (pl.tn) {
-        case 16: e = launch_tn<16>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 32: e = launch_tn<32>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 64: e = launch_tn<64>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 128: e = launch_tn<128>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 192: e = launch_tn<192>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 256: e = launch_tn<256>(pl.cg, tg, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 16: e = launch_tn<16>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 32: e = launch_tn<32>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 64: e = launch_tn<64>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 128: e = launch_tn<128>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 192: e = launch_tn<192>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 256: e = launch_tn<256>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
         default: break;
     }
     if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "scaled_mm launch failed: %s", cudaGetErrorString(e));
@@ -1282,6 +1318,19 @@ extern "C" int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked
     v.kernel = FEATHER_KERNEL_TMEM;
     return scaled_mm_impl(a, b_prepacked, scale, bias, c_list_host[0], M, N, K, ldc, output_dtype, &v, nullptr, 0, status_dev,
                           static_cast<cudaStream_t>(stream), c_list_host + 1, n_dst - 1);
+}
+
+extern "C" int feather_scaled_mm_scatter(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* const* c_list_host,
+                                         int n_dst, int64_t rows_per_dst, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype,
+                                         const feather_mm_variant* variant, int* status_dev, feather_stream_t stream) {
+    if (c_list_host == nullptr || n_dst < 1) return set_error(FEATHER_ERR_BAD_ARGUMENT, "c_list_host must hold at least one output buffer");
+    if (rows_per_dst <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "rows_per_dst must be positive");
+    feather_mm_variant v{};
+    if (variant) v = *variant;
+    v.split_k = 1;                      // blocks leave through TMA stores, which a K split through the workspace does not use
+    v.kernel = FEATHER_KERNEL_TMEM;
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c_list_host[0], M, N, K, ldc, output_dtype, &v, nullptr, 0, status_dev,
+                          static_cast<cudaStream_t>(stream), c_list_host + 1, n_dst - 1, rows_per_dst);
 }
 
 extern "C" int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
@@ -1380,5 +1429,6 @@ extern "C" int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t 
     out->transform_groups = pl.tg;
     out->max_ctas = 0;
     out->kernel = M <= 16 ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
+    out->staging = 0;
     return FEATHER_OK;
 }

@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_choose",
     "feather_scaled_mm_static",
     "feather_scaled_mm_multi",
+    "feather_scaled_mm_scatter",
+    "feather_reduce_partials",
     "feather_scaled_mm_static_scratch_bytes",
     "feather_quantize_prepack",
     "feather_prepack_bytes",
@@ -53,10 +55,11 @@ class MMVariant(ctypes.Structure):
         ("transform_groups", ctypes.c_int),
         ("max_ctas", ctypes.c_int),
         ("kernel", ctypes.c_int),
+        ("staging", ctypes.c_int),
     ]
 
     def as_tuple(self):
-        return (self.tokens_tile, self.cta_pair, self.split_k, self.transform_groups, self.max_ctas, self.kernel)
+        return (self.tokens_tile, self.cta_pair, self.split_k, self.transform_groups, self.max_ctas, self.kernel, self.staging)
 
 
 class FeatherNativeError(RuntimeError):
@@ -94,6 +97,10 @@ def load_library():
         lib.feather_scaled_mm_static.restype = ci
         lib.feather_scaled_mm_multi.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
         lib.feather_scaled_mm_multi.restype = ci
+        lib.feather_scaled_mm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
+        lib.feather_scaled_mm_scatter.restype = ci
+        lib.feather_reduce_partials.argtypes = [vp, ci, i64, i64, vp, vp, i64, ctypes.POINTER(vp), ci, i64, ci, vp]
+        lib.feather_reduce_partials.restype = ci
         lib.feather_scaled_mm_static_scratch_bytes.argtypes = []
         lib.feather_scaled_mm_static_scratch_bytes.restype = sz
         lib.feather_quantize_prepack.argtypes = [vp, ci, vp, i64, i64, ci, vp, vp, vp, vp]
@@ -309,8 +316,8 @@ def read_stats(device):
 KERNEL_AUTO, KERNEL_TMEM, KERNEL_STREAM = 0, 1, 2
 
 
-def make_variant(tokens_tile=0, cta_pair=0, split_k=0, transform_groups=0, max_ctas=0, kernel=0):
-    return MMVariant(tokens_tile, cta_pair, split_k, transform_groups, max_ctas, kernel)
+def make_variant(tokens_tile=0, cta_pair=0, split_k=0, transform_groups=0, max_ctas=0, kernel=0, staging=0):
+    return MMVariant(tokens_tile, cta_pair, split_k, transform_groups, max_ctas, kernel, staging)
 
 
 def choose_variant(M, N, K, workspace_bytes=_WORKSPACE_BYTES):
@@ -368,6 +375,48 @@ def scaled_mm_multi_into(a, b_prepacked, scale, bias, outputs, variant=None):
         )
     _check(status, "feather_scaled_mm_multi")
     return outputs[0]
+
+
+def scaled_mm_scatter_into(a, b_prepacked, scale, outputs, rows_per_dst, variant=None):
+    """Row-parallel GEMM: this rank's partial of token rows [d*rows_per_dst, (d+1)*rows_per_dst) is stored to outputs[d]
+    ([rows_per_dst, N] each, own memory or a peer's).  No bias here: it is added once, by reduce_partials_into."""
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale)
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    c0 = outputs[0]
+    for c in outputs:
+        if c.shape != c0.shape or c.stride() != c0.stride() or c.dtype != c0.dtype or c.shape[0] != rows_per_dst:
+            raise FeatherNativeError("all row-sharded output buffers must be [rows_per_dst, N] with the same strides and dtype")
+    ptrs = (ctypes.c_void_p * len(outputs))(*[c.data_ptr() for c in outputs])
+    st = status_word_for(dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_scaled_mm_scatter(
+            _ptr(a), _ptr(b_prepacked), _ptr(scale), None, ptrs, len(outputs), rows_per_dst, M, N, K, c0.stride(0), _OUT_CODE[c0.dtype],
+            ctypes.byref(variant) if variant is not None else None, _ptr(st), _stream_ptr(dev),
+        )
+    _check(status, "feather_scaled_mm_scatter")
+
+
+def reduce_partials_into(partials, bias, residual, outputs):
+    """outputs[d][r, :] = cvt(sum_s fp32(partials[s, r, :])) + bias (+ residual[r, :]) for every destination d.
+    partials [n_src, rows, N] on the current device; outputs are [rows, N] views (own memory or peers')."""
+    lib = load_library()
+    dev = _require_cuda(partials, bias, residual)
+    n_src, rows, N = partials.shape
+    if not partials.is_contiguous():
+        raise FeatherNativeError("partials must be contiguous")
+    o0 = outputs[0]
+    for o in outputs:
+        if o.shape != (rows, N) or o.stride() != o0.stride() or o.dtype != partials.dtype:
+            raise FeatherNativeError("every destination must be a [rows, N] view with the partials' dtype and equal strides")
+    ptrs = (ctypes.c_void_p * len(outputs))(*[o.data_ptr() for o in outputs])
+    with torch.cuda.device(dev):
+        status = lib.feather_reduce_partials(
+            _ptr(partials), n_src, rows, N, _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0,
+            ptrs, len(outputs), o0.stride(0), _OUT_CODE[partials.dtype], _stream_ptr(dev),
+        )
+    _check(status, "feather_reduce_partials")
 
 
 def scaled_mm_static_into(a, b_prepacked, scale, bias, c, variant=None):

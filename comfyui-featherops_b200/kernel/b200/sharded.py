@@ -1,21 +1,30 @@
-"""Column-sharded mixed-precision linear for one box of 2/4/8 GPUs: each rank keeps the weight columns
-[r*N/g, (r+1)*N/g) of the prepacked (K/16, N, 16) weight (dim 1), the activations are replicated, every rank computes
-its [M, N/g] block and the blocks are all-gathered along N.
+"""Mixed-precision linears sharded over the 2/4/8 GPUs of one box, one process per GPU.
 
-The reference has no multi-GPU path; this layer is new.  K is never split, so each output element sees the same
-additions in the same order on any number of ranks: the sharded result is bitwise the single-GPU result.
+The reference has no multi-GPU path; everything here is new.  Two shardings of the prepacked (K/16, N, 16) weight:
 
-Two exchange steps are provided:
+ColumnShardedLinear   rank r keeps the weight columns [r*N/g, (r+1)*N/g) (dim 1).  The activations are replicated, every rank
+                      computes its [M, N/g] block.  K is never split, so each output element sees the same additions in the
+                      same order on any number of ranks: the result is bitwise the single-GPU result.  Exchanges:
+    "peer_store"      fused into the GEMM.  The output is an [M, N] buffer in symmetric memory on every rank; the kernel's
+                      epilogue TMA-stores each finished block into its column range of ALL ranks' buffers while the tensor
+                      cores run the next tile (a staging ring that holds a whole tile lets NVLink take as long as the tile's
+                      MMAs).  Outputs are double-buffered per (M, dtype), so ONE cross-rank barrier per call is enough, the one
+                      after the launch ("all blocks have landed"): a rank reaches the barrier of call n only after its own
+                      stream has run everything that read the output of call n-1, so once call n's barrier has passed, nobody
+                      still reads the buffer that call n+1 overwrites.
+    "all_gather"      `all_gather_into_tensor` (NCCL) of the [M, N/g] blocks, then a relayout copy to [M, N].  Baseline.
+    "none"            no exchange: the call returns the local [M, N/g] block (first half of a tensor-parallel pair).
 
-  "all_gather"  `torch.distributed.all_gather_into_tensor` (NCCL over NVLink) delivers [g, M, N/g]; the [M, N] row-major
-                layout the next layer expects is then one strided copy.  This is the baseline.
-  "peer_store"  the exchange is fused into the GEMM: the output lives in symmetric memory (one [M, N] buffer per rank, every
-                rank can address every peer's buffer), and the kernel's epilogue TMA-stores each finished block into its
-                column range of ALL ranks' buffers while the tensor cores work on the next tile.  No separate collective, no
-                relayout copy; a cross-rank barrier before (peers are done reading the previous output) and after (all
-                stores have landed) brackets the launch.  Only stores cross NVLink; nothing loads from peer memory.
+RowShardedLinear      rank r keeps the k16-planes [r*K/16g, (r+1)*K/16g) (dim 0, a contiguous slice) and multiplies its own
+                      K/g activation columns: every rank holds a partial sum of the whole output.  The reduction is a
+                      reduce-scatter fused into the GEMM (each finished block, rounded to the output dtype, is TMA-stored to
+                      the rank that owns its token rows) followed by one small kernel that adds the g partials of the owned
+                      rows in fp32 in rank order, rounds once, adds bias and residual, and writes the rows into every rank's
+                      output (plain stores over NVLink: the all-gather).  K is split across ranks, so this is NOT bitwise
+                      the single-GPU result: the partials are rounded to 16 bits before they are summed.  It is deterministic
+                      (same bits on every rank, every run) and within the GEMM gate of the tests.
 
-With world size 1 there is no exchange and no copy.
+Only stores ever cross NVLink; no load reads peer memory.  With world size 1 there is no exchange and no copy.
 """
 
 import torch
@@ -35,9 +44,39 @@ def shard_columns(b_prepacked, bias, rank, world):
     return b_local, bias_local
 
 
+def shard_k_planes(b_prepacked, rank, world):
+    """The k16-planes of `rank`: dim 0 of (K/16, N, 16), a contiguous slice.  K/16 must divide evenly."""
+    kb = b_prepacked.shape[0]
+    if kb % world != 0:
+        raise ValueError(f"K={kb * 16} is not divisible by 16 x the number of ranks {world}")
+    per = kb // world
+    return b_prepacked[rank * per:(rank + 1) * per].contiguous()
+
+
+class _SymmetricBuffers:
+    """Double-buffered symmetric-memory tensors of one shape: entry p is (own tensor, handle, views of every rank's tensor)."""
+
+    def __init__(self, shape, dtype, device, rank, world, group):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.entries = []
+        for _ in range(2):
+            buf = symm_mem.empty(shape, dtype=dtype, device=device)
+            handle = symm_mem.rendezvous(buf, group.group_name)
+            views = [buf if r == rank else handle.get_buffer(r, shape, dtype) for r in range(world)]
+            self.entries.append((buf, handle, views))
+        self.calls = 0
+
+    def next(self):
+        entry = self.entries[self.calls & 1]
+        self.calls += 1
+        return entry
+
+
 class ColumnShardedLinear:
     def __init__(self, b_prepacked, scale, bias, rank, world, device, group=None, exchange="all_gather"):
-        if exchange not in ("all_gather", "peer_store"):
+        if exchange not in ("all_gather", "peer_store", "none"):
             raise ValueError(f"unknown exchange {exchange!r}")
         self.rank, self.world, self.group = rank, world, group
         self.exchange = exchange
@@ -65,33 +104,28 @@ class ColumnShardedLinear:
         native.scaled_mm_into(a, self.b_local, self.scale, self.bias_local, out, variant=self._variant(a.shape[0], variant))
         return out
 
-    def _symmetric_output(self, m, out_dtype, device):
-        """[m, N] output buffer in symmetric memory plus views of every rank's buffer (cached per (m, dtype))."""
-        key = (m, out_dtype)
-        entry = self._symm.get(key)
-        if entry is None:
-            import torch.distributed._symmetric_memory as symm_mem
-
-            group = self.group if self.group is not None else dist.group.WORLD
-            buf = symm_mem.empty((m, self.n_total), dtype=out_dtype, device=device)
-            handle = symm_mem.rendezvous(buf, group.group_name)
-            views = [buf if r == self.rank else handle.get_buffer(r, (m, self.n_total), out_dtype) for r in range(self.world)]
-            entry = (buf, handle, views)
-            self._symm[key] = entry
-        return entry
+    def bytes_out_per_call(self, m, itemsize=2):
+        """Bytes this rank pushes to its peers per call of the fused exchange (its block, once per peer)."""
+        return (self.world - 1) * m * self.n_local * itemsize
 
     def _peer_store(self, a, out_dtype, variant):
         m = a.shape[0]
-        buf, handle, views = self._symmetric_output(m, out_dtype, a.device)
+        key = (m, out_dtype)
+        bufs = self._symm.get(key)
+        if bufs is None:
+            bufs = self._symm[key] = _SymmetricBuffers((m, self.n_total), out_dtype, a.device, self.rank, self.world, self.group)
+        buf, handle, views = bufs.next()
         lo, hi = self.rank * self.n_local, (self.rank + 1) * self.n_local
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]      # own buffer first
+        # own buffer first, then the peers in a rotated order: at any moment the ranks' stores head for different GPUs
+        order = [(self.rank + i) % self.world for i in range(self.world)]
         outputs = [views[r][:, lo:hi] for r in order]
-        handle.barrier()                       # every rank has finished reading the previous contents of its buffer
         native.scaled_mm_multi_into(a, self.b_local, self.scale, self.bias_local, outputs, variant=variant)
         handle.barrier()                       # every rank's blocks have landed everywhere
         return buf
 
     def __call__(self, a, out_dtype, variant=None):
+        if self.exchange == "none":
+            return self.gemm_only(a, out_dtype, variant)
         if self.world > 1 and self.exchange == "peer_store":
             return self._peer_store(a, out_dtype, variant)
         local = self.gemm_only(a, out_dtype, variant)
@@ -101,3 +135,54 @@ class ColumnShardedLinear:
         gathered = torch.empty((self.world * m, self.n_local), dtype=out_dtype, device=a.device)    # rank-major concatenation
         dist.all_gather_into_tensor(gathered, local, group=self.group)
         return gathered.view(self.world, m, self.n_local).permute(1, 0, 2).reshape(m, self.n_total)
+
+
+class RowShardedLinear:
+    """y = x @ W (+ bias, + residual) with K sharded over the ranks: `a_local` holds this rank's K/g activation columns."""
+
+    def __init__(self, b_prepacked, scale, bias, rank, world, device, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        self.n = b_prepacked.shape[1]
+        self.k = b_prepacked.shape[0] * 16
+        self.b_local = shard_k_planes(b_prepacked.to(device), rank, world)
+        self.k_local = self.b_local.shape[0] * 16
+        self.scale = scale.to(device=device, dtype=torch.float32)
+        self.bias = bias.to(device) if bias is not None else None
+        self._symm = {}
+        self.launches_per_call = 1 if world == 1 else 2
+
+    def bytes_out_per_call(self, m, itemsize=2):
+        """Bytes this rank pushes to its peers per call: its partials of the rows it does not own, then its reduced rows."""
+        rows = m // self.world
+        return 2 * (self.world - 1) * rows * self.n * itemsize
+
+    def __call__(self, a_local, out_dtype, residual=None, variant=None):
+        m = a_local.shape[0]
+        if self.world == 1:
+            out = torch.empty((m, self.n), dtype=out_dtype, device=a_local.device)
+            native.scaled_mm_into(a_local, self.b_local, self.scale, self.bias, out, variant=variant)
+            if residual is not None:
+                out += residual
+            return out
+        g = self.world
+        if m % (32 * g) != 0:
+            raise ValueError(f"the row-parallel linear needs a token count divisible by 32 x the number of ranks ({32 * g}), got {m}")
+        rows = m // g
+        key = (m, out_dtype)
+        entry = self._symm.get(key)
+        if entry is None:
+            entry = self._symm[key] = (
+                _SymmetricBuffers((g, rows, self.n), out_dtype, a_local.device, self.rank, g, self.group),    # partials, one slot per source rank
+                _SymmetricBuffers((m, self.n), out_dtype, a_local.device, self.rank, g, self.group),          # reduced output
+            )
+        part, part_handle, part_views = entry[0].next()
+        out, out_handle, out_views = entry[1].next()
+        # 1. GEMM over this rank's K slice; each finished block goes to slot `rank` of the rank that owns its token rows
+        native.scaled_mm_scatter_into(a_local, self.b_local, self.scale, [part_views[d][self.rank] for d in range(g)], rows, variant=variant)
+        part_handle.barrier()                  # all g partials of my rows have landed
+        # 2. add the partials of my rows (fp32, rank order), + bias, + residual; write the rows into every rank's output
+        lo, hi = self.rank * rows, (self.rank + 1) * rows
+        order = [(self.rank + i) % g for i in range(g)]
+        native.reduce_partials_into(part, self.bias, residual[lo:hi] if residual is not None else None, [out_views[r][lo:hi] for r in order])
+        out_handle.barrier()                   # every rank's rows have landed everywhere
+        return out

@@ -60,6 +60,8 @@ enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
  *   max_ctas    : cap on the persistent grid (0 = number of SMs)
  *   kernel      : 0 = choose from the shape (streaming up to 16 tokens); 1 = the tensor-memory (tcgen05) kernel; 2 = the
  *                 register-streaming kernel, at most 32 tokens (needs no workspace, ignores the other fields)
+ *   staging     : output staging of 256-token pair tiles: 0 = choose (a ring that holds a whole tile when blocks also go to
+ *                 peer GPUs, one buffer otherwise), 1 = one buffer, 2 = the whole-tile ring
  */
 enum { FEATHER_KERNEL_AUTO = 0, FEATHER_KERNEL_TMEM = 1, FEATHER_KERNEL_STREAM = 2 };
 typedef struct feather_mm_variant {
@@ -69,6 +71,7 @@ typedef struct feather_mm_variant {
     int transform_groups;
     int max_ctas;
     int kernel;
+    int staging;
 } feather_mm_variant;
 
 /* ---------------------------------------------------------------------------------------------
@@ -112,6 +115,32 @@ FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, 
 FEATHER_API int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias,
                                         void* const* c_list_host, int n_dst, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype,
                                         const feather_mm_variant* variant, int* status_dev, feather_stream_t stream);
+
+/* Row-parallel half of a tensor-parallel pair of linears (K sharded across the GPUs of one box, so every rank holds a
+ * partial sum of the whole [M, N] output): the same launch as feather_scaled_mm_multi, but the destinations are sharded by
+ * token rows.  c_list_host[d] (a HOST array of n_dst device pointers, peer-mapped for d != own rank) receives this rank's
+ * partial of rows [d * rows_per_dst, (d + 1) * rows_per_dst) as a [rows_per_dst, ldc] row-major block, rounded to the output
+ * dtype; each finished block is TMA-stored to the one buffer that owns its rows while the tensor cores run the next tile.
+ * Every rank passes, for destination d, ITS OWN slot of rank d's buffer, so the owner ends up with one partial per rank and
+ * sums them with feather_reduce_partials.  rows_per_dst must be a multiple of 32; only stores cross NVLink.  Pass
+ * bias = NULL here and give the bias to feather_reduce_partials (it must be added once, not once per rank).
+ * The reference has no multi-GPU path; this entry point has no counterpart in the reference. */
+FEATHER_API int feather_scaled_mm_scatter(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias,
+                                          void* const* c_list_host, int n_dst, int64_t rows_per_dst, int64_t M, int64_t N, int64_t K,
+                                          int64_t ldc, int output_dtype, const feather_mm_variant* variant, int* status_dev,
+                                          feather_stream_t stream);
+
+/* Second step of the row-parallel linear: out[r][n] = cvt(sum_s fp32(partials[s][r][n])) + bias[n] (+ residual[r][n]), the sum
+ * taken in slot order s = 0 .. n_src-1 in fp32 (deterministic), one rounding to the 16-bit dtype, the bias added in that dtype
+ * as in the GEMM epilogue (kernel/naive.py:34-40 of the reference), then the optional residual (same dtype, [rows, ld_res]).
+ *   partials      [n_src][rows][N] contiguous, 16-bit dtype per `dtype` (FEATHER_OUT_*), on this GPU
+ *   dst_list_host HOST array of n_dst device pointers; the result rows are written to each (own buffer and peer-mapped
+ *                 buffers of the other ranks, plain 16-byte stores over NVLink), row pitch ld_dst elements.  This is the
+ *                 all-gather of the reduced rows: pass every rank's full output offset to this rank's first row.
+ * N must be a multiple of 8 and all pointers 16-byte aligned.  No counterpart in the reference. */
+FEATHER_API int feather_reduce_partials(const void* partials, int n_src, int64_t rows, int64_t N, const void* bias, const void* residual,
+                                        int64_t ld_res, void* const* dst_list_host, int n_dst, int64_t ld_dst, int dtype,
+                                        feather_stream_t stream);
 
 /* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K).  Pass the same
  * `variant` (or NULL) as to feather_scaled_mm_ex.  The reference's shipped kernel never splits K (README.md:31

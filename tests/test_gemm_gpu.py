@@ -76,7 +76,7 @@ def test_benchmark_distribution(golden, hip_kernel, native, cuda_dev, name):
     assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle", has_bias=c["bias"] is not None)
 
 
-# (M, N, K, out_dtype, (tokens_tile, cta_pair, split_k, transform_groups, max_ctas), bias, scale)
+# (M, N, K, out_dtype, (tokens_tile, cta_pair, split_k, transform_groups, max_ctas[, kernel, staging]), bias, scale)
 VARIANT_CASES = [
     (16, 128, 64, "fp16", (16, 1, 1, 2, 0), False, True),
     (16, 128, 128, "fp16", (16, 1, 1, 1, 0), True, True),
@@ -102,6 +102,8 @@ VARIANT_CASES = [
     (90, 250, 256, "fp16", (128, 1, 1, 2, 0), True, True),           # N % 8 != 0: rows not 16-byte aligned, plain-store epilogue
     (700, 600, 2048, "fp16", (128, 2, 1, 1, 8), True, True),        # pairs, N not a multiple of 256
     (64, 512, 4096, "fp16", (64, 2, 4, 2, 0), True, True),          # pairs + split-K
+    (3000, 1024, 512, "bf16", (256, 2, 1, 2, 8, 0, 2), True, True),  # tile-deep staging ring: 4 CTA pairs walk 48 tiles, ragged last token tile
+    (1500, 520, 256, "fp16", (256, 2, 1, 1, 4, 0, 2), True, True),  # the same with one transform group, N not a multiple of the tile
     (16, 5120, 1024, "bf16", None, True, True),                     # library-chosen variant
     (300, 1024, 1024, "bf16", None, False, True),
 ]

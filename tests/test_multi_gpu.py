@@ -1,6 +1,8 @@
-"""GPU (2 or more devices): the column-sharded linear, one process per GPU over NCCL / NVLink.  Both exchanges - the fused
-peer-store epilogue over symmetric memory and the NCCL all-gather baseline - must reproduce the single-GPU output bit for
-bit (K is never split across ranks).  Skipped on a single-GPU box."""
+"""GPU (2 or more devices): the sharded linears and the DiT harness, one process per GPU over NCCL / NVLink.  Both exchanges of
+the column-sharded linear - the fused peer-store epilogue over symmetric memory and the NCCL all-gather baseline - must
+reproduce the single-GPU output bit for bit (K is never split across ranks); the row-parallel linear (K split) must be within
+the GEMM gate and identical on all ranks; the DiT forward is bitwise in all-gather mode and within 2e-2 (Frobenius) in pairs
+mode.  Skipped on a single-GPU box."""
 
 import importlib
 import os
@@ -20,13 +22,27 @@ def _worker(rank, world, port, tmpdir):
     import torch.distributed as dist
 
     import __graft_entry__
+    from oracle import feather_oracle as fo
+    from tests.util import from_torch
 
     __graft_entry__.load_package()
     native = importlib.import_module("feather_b200.kernel.b200.native")
     sharded = importlib.import_module("feather_b200.kernel.b200.sharded")
+    dit = importlib.import_module("feather_b200.kernel.b200.dit")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    failed = []
+
+    def check(name, cond):
+        if not bool(cond):
+            failed.append(name)
+
+    def same_on_all_ranks(t):
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t.contiguous())
+        return all(torch.equal(x.view(torch.int16), gathered[0].view(torch.int16)) for x in gathered)
+
     g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: replicated activations and weights
     M, K, N = 1000, 1024, 1536
     a = torch.randn((M, K), generator=g, device=dev).to(torch.float16)
@@ -36,16 +52,56 @@ def _worker(rank, world, port, tmpdir):
     s = s.reshape(1)
     full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     native.scaled_mm_into(a, bq, s, bias, full)
-    ok = True
     for exchange in ("peer_store", "all_gather"):
         lin = sharded.ColumnShardedLinear(bq, s, bias, rank, world, dev, exchange=exchange)
-        for _ in range(2):                                    # twice: the symmetric buffer is reused
+        for call in range(3):                                 # three calls: both halves of the double-buffered output are reused
             out = lin(a, torch.bfloat16)
             torch.cuda.synchronize()
-            ok = ok and out.shape == (M, N) and torch.equal(out.view(torch.int16), full.view(torch.int16))
+            check(f"column {exchange} call {call}", out.shape == (M, N) and torch.equal(out.view(torch.int16), full.view(torch.int16)))
+    # 256-token pair tiles with the tile-deep staging ring (what the benchmark shapes use), ragged last tile
+    M3 = 8192 + 136                                           # 99 pair tiles per rank: some CTA pairs run two tiles through the ring
+    a3 = torch.randn((M3, K), generator=g, device=dev).to(torch.float16)
+    full3 = torch.empty((M3, N), dtype=torch.bfloat16, device=dev)
+    native.scaled_mm_into(a3, bq, s, bias, full3)
+    lin = sharded.ColumnShardedLinear(bq, s, bias, rank, world, dev, exchange="peer_store")
+    for call in range(3):
+        out = lin(a3, torch.bfloat16)
+        torch.cuda.synchronize()
+        check(f"column peer_store wide tiles call {call}", torch.equal(out.view(torch.int16), full3.view(torch.int16)))
+
+    # row-parallel linear (K sharded): reduce-scatter fused into the GEMM + reduce/all-gather kernel; every rank must hold the
+    # same bits, within the GEMM gate of the unsharded result (+ residual)
+    M2 = 1024
+    a2 = torch.randn((M2, K), generator=g, device=dev).to(torch.float16)
+    res = torch.randn((M2, N), generator=g, device=dev).to(torch.bfloat16)
+    full2 = torch.empty((M2, N), dtype=torch.bfloat16, device=dev)
+    native.scaled_mm_into(a2, bq, s, bias, full2)
+    full2 += res
+    row = sharded.RowShardedLinear(bq, s, bias, rank, world, dev)
+    kl = K // world
+    for call in range(3):
+        out = row(a2[:, rank * kl:(rank + 1) * kl].contiguous(), torch.bfloat16, residual=res)
+        torch.cuda.synchronize()
+        rep = fo.error_report(from_torch(out), from_torch(full2), "bf16")
+        check(f"row-parallel call {call} {rep}", rep["nonfinite_agree"] and rep["fro_rel"] <= 2e-3 and rep["max_excess_over_1ulp"] <= 1e-2 * rep["rms"])
+        check(f"row-parallel call {call} identical on all ranks", same_on_all_ranks(out))
+
+    # the DiT harness: all-gather mode is bitwise the one-rank forward, pairs mode is within tolerance and identical on all ranks
+    cfg = dit.DitConfig(hidden=1024, heads=8, head_dim=128, ffn=2816, blocks=2)
+    x = torch.randn((512, cfg.hidden), generator=g, device=dev).to(torch.bfloat16)
+    one = dit.FeatherDiT(cfg, rank=0, world=1, device=dev, mode="all_gather", seed=3)(x)
+    for exchange in ("peer_store", "all_gather"):
+        y = dit.FeatherDiT(cfg, rank=rank, world=world, device=dev, mode="all_gather", exchange=exchange, seed=3)(x)
+        torch.cuda.synchronize()
+        check(f"dit all_gather/{exchange} bitwise", torch.equal(y.view(torch.int16), one.view(torch.int16)))
+    yp = dit.FeatherDiT(cfg, rank=rank, world=world, device=dev, mode="pairs", seed=3)(x).clone()
+    torch.cuda.synchronize()
+    fro = float((yp.float() - one.float()).norm() / one.float().norm())
+    check(f"dit pairs fro_rel {fro:.3e}", fro <= 2e-2)
+    check("dit pairs identical on all ranks", same_on_all_ranks(yp))
     native.check_device_status(dev)
     with open(os.path.join(tmpdir, f"ok{rank}"), "w") as f:
-        f.write("1" if ok else "0")
+        f.write("ok" if not failed else "FAILED: " + "; ".join(failed))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -55,4 +111,4 @@ def test_column_sharded_linear_two_gpus(tmp_path):
         pytest.skip("needs at least 2 GPUs")
     port = 29600 + (os.getpid() % 1000)
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    assert [open(tmp_path / f"ok{r}").read() for r in range(2)] == ["1", "1"]
+    assert [open(tmp_path / f"ok{r}").read() for r in range(2)] == ["ok", "ok"]
