@@ -6,13 +6,21 @@
 
 A step is one pass over the workload's linears (default: the three Wan-2.1-14B shapes at M = 32768 tokens, bf16 out).
 One JSON line is printed by rank 0.  For N > 1 (launched with torch.distributed.run) every GEMM is sharded by weight
-columns across the ranks and followed by an all-gather of the output over NCCL.
+columns across the ranks and its output exchanged: by default the GEMM's own epilogue TMA-stores every finished block into
+all ranks' output buffers over NVLink (`--exchange peer_store`); `--exchange all_gather` is the NCCL all-gather baseline.
+After the warm-up, and outside the timed region, every rank compares rows of each exchanged output bit for bit with an
+unsharded GEMM of the same rows (`exchange_check` in the line; a mismatch fails the run).
 
-Other workloads (not the driver's line): --workload qwen | smallm | quant, or --shape M,N,K for a single GEMM.
+The N = 1 line also carries `small_m`: GB/s of the bandwidth-bound shapes (M in {1, 16, 128}), CUDA-graph replay.
+
+Other workloads (not the driver's line): --workload qwen | smallm | quant | dit, or --shape M,N,K for a single GEMM.
+`--workload dit` is the 4-block Wan-like DiT forward (32768 tokens) whose linears are all Feather linears; `--dit-mode pairs`
+runs it as tensor-parallel pairs (column-parallel -> row-parallel) instead of an all-gather after every linear.
 """
 
 import argparse
 import importlib
+import importlib.util
 import json
 import os
 import statistics
@@ -104,7 +112,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wan", choices=["wan", "qwen", "smallm", "quant"])
+    ap.add_argument("--workload", default="wan", choices=["wan", "qwen", "smallm", "quant", "dit"])
+    ap.add_argument("--dit-mode", default="all_gather", choices=["all_gather", "pairs"])
+    ap.add_argument("--tokens", type=int, default=32768, help="dit: token count")
+    ap.add_argument("--blocks", type=int, default=4, help="dit: transformer blocks")
+    ap.add_argument("--no-small-m", action="store_true", help="skip the small_m sub-record of the default N = 1 line")
     ap.add_argument("--shape", default=None, help="M,N,K: time a single GEMM instead of a workload")
     ap.add_argument("--variant", default=None, help="tokens_tile,cta_pair,split_k,transform_groups,max_ctas (0 = auto)")
     ap.add_argument("--out-dtype", default=None, choices=["bf16", "fp16"])
@@ -132,10 +144,41 @@ def shapes_for(args):
                                           "qwen": "Qwen-Image MMDiT linears, M=4352"}[args.workload]
 
 
+def config_for(args, M, kn_list, out_dtype, desc, world):
+    """The `config` object of the JSON line; both arms print the same one for the same arguments."""
+    step_mb = sum(2.0 * M * K + K * N + 2.0 * M * N for K, N in kn_list) / 1e6
+    l2 = (f"one step touches {step_mb:.0f} MB over {len(kn_list)} linears "
+          + ("(larger than the 126 MB L2, so no launch finds its inputs cached); no flush needed" if step_mb > 252
+             else "(not larger than twice the 126 MB L2 and no flush between launches: a probe shape, not a bench line)"))
+    if world == 1:
+        par = "single GPU"
+    elif args.exchange == "peer_store":
+        par = (f"weights sharded by output columns over {world} GPUs; each rank's epilogue TMA-stores its blocks into every rank's output "
+               "over NVLink (fused exchange), one cross-rank barrier per linear")
+    else:
+        par = f"weights sharded by output columns over {world} GPUs; NCCL all-gather of the output + relayout"
+    return {"workload": desc, "out_dtype": out_dtype, "l2": l2, "parallelism": par, "variant": args.variant or "auto"}
+
+
 # ------------------------------------------------------------------------------------------------------
-# CPU arm: the reference's naive torch path (oracle/naive_torch.py restates kernel/naive.py; fp32 product)
+# CPU arm: the reference's naive torch path.  The reference's own kernel/naive.py is used when a copy of the reference is
+# at hand ($FEATHER_REFERENCE_DIR or baseline/_ref); otherwise oracle/naive_torch.py, which restates it.
 # ------------------------------------------------------------------------------------------------------
-def time_cpu_step(kn_list, out_dtype, rows, repeats=1, warm=True):
+def find_reference_naive():
+    """The reference's `scaled_mm_naive` loaded by path from its own kernel/naive.py, or None."""
+    for base in (os.environ.get("FEATHER_REFERENCE_DIR"), os.path.join(ROOT, "baseline", "_ref")):
+        if not base:
+            continue
+        path = os.path.join(base, "kernel", "naive.py")
+        if os.path.exists(path):
+            spec = importlib.util.spec_from_file_location("feather_reference_naive", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            return mod.scaled_mm_naive, path
+    return None, None
+
+
+def time_cpu_step(kn_list, out_dtype, rows, repeats=1, warm=True, reference_fn=None):
     from oracle import naive_torch
 
     torch.manual_seed(0)
@@ -146,14 +189,20 @@ def time_cpu_step(kn_list, out_dtype, rows, repeats=1, warm=True):
         b, s = naive_torch.quantize_prepack_cpu(w)
         cases.append((a, b, s))
     flops = sum(2.0 * rows * K * N for K, N in kn_list)
+
+    def one(a, b, s):
+        if reference_fn is not None:
+            return reference_fn(a, b, s, None, TORCH_DT[out_dtype], b_prepacked=True)
+        return naive_torch.scaled_mm_cpu(a, b, s, None, TORCH_DT[out_dtype])
+
     if warm:
         a, b, s = cases[0]
-        naive_torch.scaled_mm_cpu(a[:64], b, s, None, TORCH_DT[out_dtype])
+        one(a[:64], b, s)
     times = []
     for _ in range(repeats):
         t0 = time.perf_counter()
         for a, b, s in cases:
-            naive_torch.scaled_mm_cpu(a, b, s, None, TORCH_DT[out_dtype])
+            one(a, b, s)
         times.append(time.perf_counter() - t0)
     t = statistics.median(times)
     return flops / t / 1e12, t, flops
@@ -167,16 +216,29 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     rows = min(args.cpu_sample_rows, M)
+    ref_fn, ref_path = find_reference_naive()
     for _ in range(max(args.warmup, 1) - 1):
         time_cpu_step(kn_list, out_dtype, min(rows, 256), warm=False)
-    tflops, t, _ = time_cpu_step(kn_list, out_dtype, rows, repeats=max(1, min(args.steps, 3)))
-    sample = f"{rows} of {M} token rows of each linear per step (kernel/naive.py op sequence, fp32 product), median of {max(1, min(args.steps, 3))} steps"
+    reps = max(1, min(args.steps, 3))
+    tflops, t, _ = time_cpu_step(kn_list, out_dtype, rows, repeats=reps)
+    kind, extra = "port", {}
+    sample = f"{rows} of {M} token rows of each linear per step (kernel/naive.py op sequence, fp32 product), median of {reps} steps"
+    if ref_fn is not None:
+        # the reference's own file, verbatim (its fp16 product overflows at this weight scale; the time is what counts here)
+        v_ref, t_ref, _ = time_cpu_step(kn_list, out_dtype, min(rows, 512), repeats=1, reference_fn=ref_fn)
+        extra = {"port_value": tflops, "reference_file": "kernel/naive.py (verbatim, fp16 product)", "reference_rows": min(rows, 512)}
+        # the faster of the two stands as the baseline, so the GPU/CPU ratio is never flattered by a slow fp16 CPU matmul
+        if v_ref >= tflops:
+            tflops, t, rows_used, kind = v_ref, t_ref, min(rows, 512), "reference"
+            sample = f"{rows_used} of {M} token rows of each linear, the reference's own kernel/naive.py loaded by path"
+            rows = rows_used
     line = {
         "impl": "reference", "metric": "TFLOPS fp16@fp8e5m2 scaled_mm at Wan-14B shapes", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3 * (M / rows), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp16xfp8e5m2->fp32", "data": "synthetic",
-        "config": {"workload": desc, "out_dtype": out_dtype, "timing": "host wall clock on a bounded row sample; ms_per_step extrapolated linearly in M"},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "config": config_for(args, M, kn_list, out_dtype, desc, args.gpus),
+        "timing": "host wall clock on a bounded row sample; ms_per_step extrapolated linearly in M",
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind, "sample": sample, **extra},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -205,9 +267,16 @@ def run_ours(args):
     native.load_library()
 
     if args.workload == "smallm" and not args.shape:
-        return run_smallm(args, native, dev)
+        rows = run_smallm(args, native, dev, Ms=(1, 8, 16, 64, 128))
+        peaks = load_peaks()
+        print(json.dumps({"metric": "GB/s fp16@fp8e5m2 scaled_mm at M<=128", "unit": "GB/s", "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                          "config": {"workload": "small-M sweep, 4 rotating weight copies (283 MB > L2); us = CUDA-graph replay, us_eager = per-call launches"},
+                          "rows": rows}), flush=True)
+        return
     if args.workload == "quant" and not args.shape:
         return run_quant(args, native, dev)
+    if args.workload == "dit" and not args.shape:
+        return run_dit(args, native, dev, world, rank, local)
 
     M, kn_list, out_dtype, desc = shapes_for(args)
     odt = TORCH_DT[out_dtype]
@@ -221,17 +290,51 @@ def run_ours(args):
         bq, s = native.quantize_prepack(w)      # loader path: fp32 in, scale = amax / 57344
         del w
         lin = sharded.ColumnShardedLinear(bq, s.reshape(1), None, rank, world, dev, exchange=args.exchange)
-        layers.append((a, lin, K, N))
+        layers.append((a, lin, K, N, bq if world > 1 else None))
     torch.cuda.synchronize()
 
-    def step():
-        for a, lin, K, N in layers:
+    def step(events=None):
+        for a, lin, K, N, _ in layers:
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record()
             lin(a, odt, variant=variant)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                events.append((e0, e1))
 
-    launches_per_step = sum(lin.launches_per_call for _, lin, _, _ in layers)
+    launches_per_step = sum(lin.launches_per_call for _, lin, _, _, _ in layers)
     for _ in range(args.warmup):
         step()
     native.check_device_status(dev)
+
+    # The exchanged outputs are checked before anything is timed: on every rank, rows of each [M, N] output against an unsharded
+    # GEMM of the same rows on that rank (K is never split, so they must agree bit for bit); MIN over the ranks.
+    exchange_check = None
+    if world > 1:
+        rows_checked, equal = 0, True
+        for a, lin, K, N, bq_full in layers:
+            out = lin(a, odt, variant=variant)
+            for r0 in sorted({(rank * (M // world)) & ~255, max(M - 300, 0), ((rank + 1) * 1000) % max(M - 256, 1)}):
+                r1 = min(r0 + 256, M)
+                ref = torch.empty((r1 - r0, N), dtype=odt, device=dev)
+                # the same tile class as the sharded launch (the variant chosen for the full token count), so the k-blocks are added in the same order
+                native.scaled_mm_into(a[r0:r1], bq_full, lin.scale, None, ref, variant=lin._variant(M, variant))
+                equal = equal and torch.equal(out[r0:r1].view(torch.int16), ref.view(torch.int16))
+                rows_checked += r1 - r0
+        flag = torch.tensor([1 if equal else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        exchange_check = {"bitwise_equal": bool(flag.item()), "layers": len(layers), "rows": rows_checked, "ranks": world,
+                          "what": "rows of every exchanged [M,N] output on every rank against an unsharded GEMM of the same rows on that rank"}
+        for i in range(len(layers)):                       # the full weights were only needed for the check
+            layers[i] = layers[i][:4] + (None,)
+        torch.cuda.empty_cache()
+        if not exchange_check["bitwise_equal"]:
+            if rank == 0:
+                print(json.dumps({"error": "exchange_check failed: an exchanged output differs from the unsharded GEMM", "exchange_check": exchange_check}), flush=True)
+            dist.destroy_process_group()
+            raise SystemExit(3)
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -240,10 +343,11 @@ def run_ours(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    launch_events = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step()
+        step(launch_events if world == 1 else None)
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -257,16 +361,13 @@ def run_ours(args):
         ms = float(t.item())
     ms_per_step = ms / args.steps
     flops_step = sum(2.0 * M * K * N for K, N in kn_list)
-    # bytes one step touches (activations, weights, outputs of all its linears) against the 126 MB L2
-    step_mb = sum(2.0 * M * K + K * N + 2.0 * M * N for K, N in kn_list) / 1e6
-    l2_note = (f"one step touches {step_mb:.0f} MB over {len(kn_list)} linears "
-               + ("(larger than the 126 MB L2, so no launch finds its inputs cached)" if step_mb > 252 else "(not larger than twice the 126 MB L2 and no flush between launches: a probe shape, not a bench line)"))
     tflops = flops_step / (ms_per_step * 1e-3) / 1e12
 
-    # per-GEMM kernel time on this rank (events on the launching stream), for the roofline line
-    gemm_ms = 0.0
+    # per-GEMM kernel time on this rank (events on the launching stream): inside the timed region on one GPU (an event pair
+    # around every launch), and as a short burst per shape, which is also what a sharded run reports for its local GEMMs
     per_shape = []
-    for a, lin, K, N in layers:
+    burst_ms = 0.0
+    for li, (a, lin, K, N, _) in enumerate(layers):
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = max(3, min(args.steps, 10))
         torch.cuda.synchronize()
@@ -276,28 +377,57 @@ def run_ours(args):
         k1.record()
         torch.cuda.synchronize()
         t_ms = k0.elapsed_time(k1) / reps
-        gemm_ms += t_ms
-        per_shape.append({"K": K, "N": N, "ms": round(t_ms, 4), "tflops": round(2.0 * M * K * (N // world) / (t_ms * 1e-3) / 1e12, 1)})
+        burst_ms += t_ms
+        row = {"K": K, "N": N, "ms_burst": round(t_ms, 4), "tflops_burst": round(2.0 * M * K * (N // world) / (t_ms * 1e-3) / 1e12, 1)}
+        if launch_events:
+            mine = [launch_events[i] for i in range(li, len(launch_events), len(layers))]
+            t_in = sum(x.elapsed_time(y) for x, y in mine) / len(mine)
+            row.update({"ms": round(t_in, 4), "tflops": round(2.0 * M * K * N / (t_in * 1e-3) / 1e12, 1)})
+        per_shape.append(row)
     peaks = load_peaks()
     local_flops = flops_step / world
-    achieved = local_flops / (gemm_ms * 1e-3) / 1e12
+    achieved_burst = local_flops / (burst_ms * 1e-3) / 1e12
+    if launch_events:
+        in_step_ms = sum(x.elapsed_time(y) for x, y in launch_events) / args.steps
+        achieved = local_flops / (in_step_ms * 1e-3) / 1e12
+        achieved_how = "sum of the CUDA-event durations of the three GEMM launches inside the timed region, averaged over the timed steps"
+    else:
+        achieved = achieved_burst
+        achieved_how = "local GEMMs of this rank timed without the exchange, 3-10 launches in a row per shape"
     timed_seconds = ms * 1e-3
     peak = peaks["tflops_sustained"] if timed_seconds >= 2.0 else peaks["tflops"]
-    # DRAM bytes per launch of the dominant kernel from the ncu capture in profiles/ (278.9 MB at M = 4096, N = 13824,
-    # K = 5120), scaled by the token count for the ffn-up launch of this run; null for other workloads.
-    traffic = 278.9e6 * (M / 4096.0) if (not args.shape and args.workload == "wan" and world == 1) else None
+    # DRAM traffic of the dominant launch (ffn-up): measured by ncu at M = 4096 (profiles/scaled_mm_kernel_m4096_n13824_k5120_full.md),
+    # 1.23 x that launch's algorithmic bytes (weight tiles are re-read after output writes evicted them from L2); the ratio is
+    # applied to the algorithmic bytes of this run's ffn-up launch, since both grow with the token count.
+    alg_ffn_up = 2.0 * M * 5120 + 5120 * 13824 + 2.0 * M * 13824
+    traffic = 1.23 * alg_ffn_up if (not args.shape and args.workload == "wan" and world == 1) else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
-        "traffic_note": "ncu dram read+write of the (5120,13824) launch at M=4096, scaled by M/4096; algorithmic bytes of that launch: 1.31e9",
-        "kernel": "scaled_mm_kernel", "peak_source": f"{peaks['source']} cuBLAS bf16, {'sustained' if timed_seconds >= 2.0 else 'burst'}",
+        "traffic_note": "dram read+write of the (5120,13824) launch: ncu measured 1.23 x the algorithmic bytes at M=4096 (profiles/scaled_mm_kernel_m4096_n13824_k5120_full.md); "
+                        f"applied to this launch's algorithmic bytes {alg_ffn_up:.3e}",
+        "kernel": "scaled_mm_kernel", "achieved_how": achieved_how, "achieved_burst": achieved_burst,
+        "peak_source": f"{peaks['source']} cuBLAS bf16, {'sustained' if timed_seconds >= 2.0 else 'burst'}",
         "frac_of_burst": achieved / peaks["tflops"], "frac_of_sustained": achieved / peaks["tflops_sustained"],
-        "frac_of_nominal_2250": achieved / 2250.0, "per_shape": per_shape,
+        "frac_of_nominal_2250": achieved / 2250.0, "frac_step_of_burst": (tflops / world) / peaks["tflops"], "per_shape": per_shape,
     }
+
+    exchange = None
+    if world > 1 and args.exchange == "peer_store":
+        out_bytes = sum(lin.bytes_out_per_call(M) for _, lin, _, _, _ in layers)
+        exchange = {"bytes_out_per_rank": out_bytes, "bytes_in_per_rank": out_bytes, "gbs_per_rank": out_bytes / (ms_per_step * 1e-3) / 1e9,
+                    "nvlink_peer_copy_gbs": 770.0, "frac_of_peer_copy": out_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0,
+                    "note": "each rank sends its column block of every output to each peer and receives theirs; the step cannot be shorter than bytes_in / link bandwidth"}
 
     # end to end through the operator with host buffers: pinned H2D of the activations, D2H of the output, every step
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps=max(2, min(args.steps, 5)))
+        e2e = run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps=max(2, min(args.steps, 5)), variant=variant)
+
+    small_m = None
+    if world == 1 and args.workload == "wan" and not args.shape and not args.no_small_m:
+        small_m = {"unit": "GB/s", "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                   "how": "algorithmic bytes 2MK+KN+2MN over the CUDA-graph replay time per launch; 4 rotating weight copies (283 MB > L2)",
+                   "rows": run_smallm(args, native, dev, Ms=(1, 16, 128), steps=20)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -312,25 +442,35 @@ def run_ours(args):
             "metric": "TFLOPS fp16@fp8e5m2 scaled_mm at Wan-14B shapes", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp16xfp8e5m2->fp32", "data": "synthetic",
-            "config": {"workload": desc, "out_dtype": out_dtype, "l2": l2_note,
-                       "parallelism": "single GPU" if world == 1 else (
-                           f"weights sharded by output columns over {world} GPUs; " + ("each rank's epilogue TMA-stores its blocks into every rank's output over NVLink (fused exchange)"
-                                                                                      if args.exchange == "peer_store" else "NCCL all-gather of the output + relayout")),
-                       "variant": args.variant or "auto"},
+            "config": config_for(args, M, kn_list, out_dtype, desc, world),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         }
+        if exchange_check is not None:
+            line["exchange_check"] = exchange_check
+        if exchange is not None:
+            line["exchange"] = exchange
+        if small_m is not None:
+            line["small_m"] = small_m
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps):
-    """Same step through `scaled_mm_hip` with HOST activations and outputs: H2D + kernel + D2H inside the timed region."""
+def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps, variant=None):
+    """The same step with HOST activations and outputs: H2D + kernel + D2H inside the timed region, every step.
+
+    One GPU: through the operator `scaled_mm_hip`, each linear in four row chunks on copy-in / GEMM / copy-out streams.
+    Several GPUs: the host holds each activation once, so every rank uploads only its M/g rows and the rows are all-gathered
+    over NVLink (NCCL); the sharded linear runs; every rank downloads its M/g rows of the exchanged output.  The box as a
+    whole still moves every activation byte up and every output byte down, once, every step.
+    """
     import torch.distributed as dist
 
+    if world > 1:
+        return run_e2e_sharded(layers, native, odt, dev, world, rank, flops_step, steps, variant)
     host = []
     h2d = d2h = 0
-    for a, lin, K, N in layers:
+    for a, lin, K, N, _ in layers:
         ha = torch.empty(a.shape, dtype=a.dtype, pin_memory=True)
         ha.copy_(a)
         hc = torch.empty((a.shape[0], lin.n_local), dtype=odt, pin_memory=True)
@@ -343,13 +483,13 @@ def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps):
     s_in, s_mm, s_out = (torch.cuda.Stream(dev) for _ in range(3))
     chunks = 4
     staging = []
-    for a, lin, K, N in layers:
+    for a, lin, K, N, _ in layers:
         rows = (a.shape[0] + chunks - 1) // chunks
         staging.append((rows, [torch.empty((rows, a.shape[1]), dtype=a.dtype, device=dev) for _ in range(2)]))
     mm_done = {}
 
     def e2e_step():
-        for li, ((ha, hc), (a, lin, K, N)) in enumerate(zip(host, layers)):
+        for li, ((ha, hc), (a, lin, K, N, _)) in enumerate(zip(host, layers)):
             rows, bufs = staging[li]
             for c in range(chunks):
                 r0, r1 = c * rows, min((c + 1) * rows, ha.shape[0])
@@ -376,26 +516,83 @@ def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps):
 
     e2e_step()
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
         e2e_step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     native.check_device_status(dev)
-    if world > 1:
-        t = torch.tensor([dt], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
     return {"value": flops_step * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "note": "weights stay resident on the GPU; activations come from and outputs return to pinned host memory every step, in 4 row chunks per linear on copy-in / GEMM / copy-out streams"}
 
 
-def run_smallm(args, native, dev):
-    """Bandwidth-bound sweep: M in {1,16,128} x {(5120,13824),(13824,5120)}, GB/s of algorithmic bytes.  Four weight
-    copies (> L2 in total) are rotated so the weight is read from HBM, not from L2."""
+def run_e2e_sharded(layers, native, odt, dev, world, rank, flops_step, steps, variant):
+    import torch.distributed as dist
+
+    host, dev_bufs = [], []
+    h2d = d2h = 0
+    for a, lin, K, N, _ in layers:
+        M = a.shape[0]
+        rows = M // world
+        r0 = rank * rows
+        ha = torch.empty((rows, K), dtype=a.dtype, pin_memory=True)
+        ha.copy_(a[r0:r0 + rows])
+        hc = torch.empty((rows, N), dtype=odt, pin_memory=True)
+        host.append((ha, hc, r0, rows))
+        dev_bufs.append((torch.empty((rows, K), dtype=a.dtype, device=dev), torch.empty((world * rows, K), dtype=a.dtype, device=dev)))
+        h2d += ha.numel() * ha.element_size()
+        d2h += hc.numel() * hc.element_size()
+    s_in, s_mm, s_out = (torch.cuda.Stream(dev) for _ in range(3))
+    done = {}
+
+    def e2e_step():
+        for li, ((ha, hc, r0, rows), (a, lin, K, N, _)) in enumerate(zip(host, layers)):
+            mine, full = dev_bufs[li]
+            with torch.cuda.stream(s_in):
+                if li in done:
+                    s_in.wait_event(done[li])                 # the GEMM that read `full` in the previous step is done
+                mine.copy_(ha, non_blocking=True)
+                dist.all_gather_into_tensor(full, mine)       # rank-major concatenation of row blocks = the [M, K] activations
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            with torch.cuda.stream(s_mm):
+                s_mm.wait_event(ev_in)
+                out = lin(full, odt, variant=variant)
+                ev_mm = torch.cuda.Event()
+                ev_mm.record(s_mm)
+                done[li] = ev_mm
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_mm)
+                hc.copy_(out[r0:r0 + rows], non_blocking=True)
+                ev_out = torch.cuda.Event()
+                ev_out.record(s_out)
+            # the exchanged output is double-buffered inside the linear: its next overwrite is two calls away, and this copy is
+            # ordered before it by making the GEMM stream wait for the copy
+            s_mm.wait_event(ev_out)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    native.check_device_status(dev)
+    t = torch.tensor([dt], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item())
+    return {"value": flops_step * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+            "h2d_bytes_per_step_per_rank": h2d, "d2h_bytes_per_step_per_rank": d2h,
+            "note": "weights stay resident; every step each rank uploads its M/g rows of every activation from pinned host memory, the rows are all-gathered over "
+                    "NVLink (NCCL), the sharded linear runs with the fused exchange, and each rank downloads its M/g rows of the output; bytes are totals over the ranks"}
+
+
+def run_smallm(args, native, dev, Ms=(1, 8, 16, 64, 128), steps=None):
+    """Bandwidth-bound sweep: M x {(5120,13824),(13824,5120)}, GB/s of algorithmic bytes.  Four weight copies (> L2 in total)
+    are rotated so the weight is read from HBM, not from L2.  Returns one row per (M, K, N)."""
     peaks = load_peaks()
+    steps = steps if steps is not None else args.steps
     rows = []
     for K, N in ((5120, 13824), (13824, 5120)):
         g = torch.Generator(device=dev).manual_seed(0)
@@ -404,10 +601,11 @@ def run_smallm(args, native, dev):
         del w
         copies = [bq] + [bq.clone() for _ in range(3)]
         s = s.reshape(1)
-        for M in (1, 8, 16, 64, 128):
+        for M in Ms:
             a = torch.randn((M, K), generator=g, device=dev).to(torch.float16)
             c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-            variant = native.make_variant(*[int(x) for x in args.variant.split(",")]) if args.variant else None
+            variant = native.make_variant(*[int(x) for x in args.variant.split(",")]) if (args.variant and args.workload == "smallm") else None
+
             def sweep():
                 for b in copies:
                     native.scaled_mm_into(a, b, s, None, c, variant=variant)
@@ -417,11 +615,11 @@ def run_smallm(args, native, dev):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 sweep()
             e1.record()
             torch.cuda.synchronize()
-            us_eager = e0.elapsed_time(e1) * 1e3 / (args.steps * len(copies))
+            us_eager = e0.elapsed_time(e1) * 1e3 / (steps * len(copies))
             # the same launches replayed from a CUDA graph: kernel time without the host's per-call cost
             graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
             with torch.cuda.stream(side):
@@ -434,19 +632,107 @@ def run_smallm(args, native, dev):
                 graph.replay()
             torch.cuda.synchronize()
             e0.record()
-            for _ in range(args.steps):
+            for _ in range(steps):
                 graph.replay()
             e1.record()
             torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (args.steps * 5 * len(copies))
+            us = e0.elapsed_time(e1) * 1e3 / (steps * 5 * len(copies))
             nbytes = 2 * M * K + K * N + 2 * M * N + 4
             v = native.choose_variant(M, N, K)
             rows.append({"M": M, "K": K, "N": N, "us": round(us, 2), "us_eager": round(us_eager, 2), "gbs": round(nbytes / us / 1e3, 1),
                          "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3), "tflops": round(2.0 * M * N * K / us / 1e6, 2),
                          "kernel": {1: "tensor-memory", 2: "streaming"}.get(v.kernel, "auto"), "variant": v.as_tuple()})
+            del graph
+        del copies
     native.check_device_status(dev)
-    print(json.dumps({"metric": "GB/s fp16@fp8e5m2 scaled_mm at M<=128", "unit": "GB/s", "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
-                      "config": {"workload": "small-M sweep, 4 rotating weight copies (283 MB > L2); us = CUDA-graph replay, us_eager = per-call launches"}, "rows": rows}), flush=True)
+    torch.cuda.empty_cache()
+    return rows
+
+
+def run_dit(args, native, dev, world, rank, local):
+    """The random-init 4-block Wan-like DiT forward (hidden 5120, 40 x 128 heads, FFN 13824 GELU, RMSNorm, torch SDPA, bf16
+    compute) with every linear a Feather e5m2 linear; one forward per step.  Reports model TFLOP/s (linears + attention) and
+    where the time goes (a second, instrumented pass with a device synchronisation around each part)."""
+    import torch.distributed as dist
+
+    dit = importlib.import_module("feather_b200.kernel.b200.dit")
+    cfg = dit.DitConfig(blocks=args.blocks)
+    T = args.tokens
+    model = dit.FeatherDiT(cfg, rank=rank, world=world, device=dev, mode=args.dit_mode, exchange=args.exchange, seed=0)
+    x = torch.randn((T, cfg.hidden), generator=torch.Generator(device=dev).manual_seed(1), device=dev).to(torch.bfloat16)
+    torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 1)):
+        y = model(x)
+    native.check_device_status(dev)
+    check = None
+    if world > 1:
+        # every rank must hold the same output; in all-gather mode it is also bitwise the one-rank forward (tests/test_multi_gpu.py)
+        gathered = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(gathered, y.contiguous())
+        same = all(torch.equal(t.view(torch.int16), gathered[0].view(torch.int16)) for t in gathered)
+        check = {"identical_on_all_ranks": bool(same), "finite": bool(torch.isfinite(y.float()).all().item())}
+        del gathered
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = model(x)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    native.check_device_status(dev)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # where the time goes: the linears alone (their inputs captured by a hook, replayed back to back, exchange included)
+    captured = []
+    model(x, hook=lambda name, i, a16, out: captured.append((name, i, a16)) if i == 0 else None)
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    blk = model.blocks[0]
+    if world > 1:
+        dist.barrier()
+    k0.record()
+    for _ in range(3):
+        for name, _, a16 in captured:
+            kw = {"residual": x} if (args.dit_mode == "pairs" and name in ("o", "down")) else {}
+            blk[name](a16, torch.bfloat16, **kw)
+    k1.record()
+    torch.cuda.synchronize()
+    lin_ms_block = k0.elapsed_time(k1) / 3
+    lin_flops = cfg.linear_flops(T)
+    attn_flops = cfg.attention_flops(T)
+    peaks = load_peaks()
+    if rank == 0:
+        total = (lin_flops + attn_flops) / (ms_per_step * 1e-3) / 1e12
+        line = {
+            "metric": "model TFLOP/s of the 4-block Wan-like DiT forward (Feather e5m2 linears + torch SDPA)", "value": total, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 activations; linears fp16xfp8e5m2->fp32->bf16", "data": "synthetic",
+            "config": {"workload": f"{cfg.blocks}-block Wan-like DiT forward, {T} tokens, hidden {cfg.hidden}, {cfg.heads}x{cfg.head_dim} heads, FFN {cfg.ffn} GELU, RMSNorm, torch SDPA",
+                       "mode": args.dit_mode, "exchange": args.exchange if args.dit_mode == "all_gather" else "reduce-scatter fused into the row-parallel GEMM + reduce/all-gather kernel",
+                       "l2": "activations of one block exceed the 126 MB L2 many times over; no flush needed"},
+            "flops": {"linears": lin_flops, "attention": attn_flops},
+            "linears": {"ms_per_block_with_exchange": lin_ms_block, "tflops_whole_job": lin_flops / cfg.blocks / (lin_ms_block * 1e-3) / 1e12,
+                        "frac_of_g_x_burst_peak": lin_flops / cfg.blocks / (lin_ms_block * 1e-3) / 1e12 / (world * peaks["tflops"]),
+                        "share_of_step": lin_ms_block * cfg.blocks / ms_per_step},
+            "rank_check": check, "gpu_launches": sum(lin.launches_per_call for _, _, lin in model.linears()) * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_quant(args, native, dev):

@@ -78,6 +78,28 @@ def build_library(force=False, verbose=False):
     return LIB_PATH
 
 
+CBENCH_SRC = os.path.join(PKG_DIR, "cbench", "bench_scaled_mm.c")
+CBENCH_BIN = os.path.join(PKG_DIR, "cbench", "bench_scaled_mm")
+
+
+def build_cbench(cc=None):
+    """Compile cbench/bench_scaled_mm.c - plain C against include/feather_b200.h, linked with the library and the CUDA runtime."""
+    build_library()
+    cc = cc or shutil.which("cc") or shutil.which("gcc")
+    if cc is None:
+        raise RuntimeError("no C compiler found")
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    cmd = [cc, "-std=c99", "-O2", "-Wall", "-Wextra", "-pedantic", CBENCH_SRC, "-I", os.path.join(PKG_DIR, "..", "include"), "-I", os.path.join(cuda, "include"),
+           "-L", PKG_DIR, "-lfeather_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-Wl,-rpath," + PKG_DIR,
+           "-Wl,-rpath," + os.path.join(cuda, "lib64"), "-o", CBENCH_BIN]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"C harness failed to build:\n{res.stdout}")
+    return CBENCH_BIN
+
+
 if __name__ == "__main__":
     path = build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    if "--cbench" in sys.argv:
+        print(build_cbench())

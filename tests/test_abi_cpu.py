@@ -2,6 +2,7 @@
 validation that needs no device returns error codes instead of faulting."""
 
 import ctypes
+import importlib.util
 import os
 import re
 
@@ -77,3 +78,30 @@ def test_cpu_tensors_are_rejected(native):
         native.scaled_mm_into(a, b, None, None, c)
     with pytest.raises(native.FeatherNativeError, match="no CPU path"):
         native.quantize_prepack(torch.zeros((16, 16)))
+
+
+def test_header_compiles_as_c_and_the_c_harness_builds(tmp_path):
+    """include/feather_b200.h is a C header (C99, pedantic, no CUDA include needed), and the plain-C timing program in
+    cbench/ compiles and links against it and the library (the counterpart of the reference's cpp_benchmarks/
+    benchmark_scaled_mm_hip.cpp, which declares the launcher itself, :27-45)."""
+    import shutil
+    import subprocess
+
+    cc = shutil.which("cc") or shutil.which("gcc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    probe = tmp_path / "probe.c"
+    probe.write_text('#include "feather_b200.h"\nint main(void) { feather_mm_variant v = {0}; return (int)sizeof(v) - 28 + (int)FEATHER_OK; }\n')
+    res = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(probe)],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert res.returncode == 0, res.stdout
+    spec = importlib.util.spec_from_file_location("feather_b200_build", os.path.join(ROOT, "comfyui-featherops_b200", "build.py"))
+    builder = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(builder)
+    try:
+        binary = builder.build_cbench()
+    except RuntimeError as e:
+        if "nvcc not found" in str(e):
+            pytest.skip("no CUDA toolkit")
+        raise
+    assert os.path.exists(binary)

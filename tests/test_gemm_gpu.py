@@ -380,3 +380,23 @@ def test_qwen_image_shapes(native, cuda_dev, K, N):
     got = _run(native, cuda_dev, a, bq, s, None, "fp16")
     rows = np.arange(0, M, 68)
     assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}", has_bias=False)
+
+
+@pytest.mark.parametrize("args", [["300", "520", "1040", "--bias", "--check", "--iters", "5"], ["16", "1024", "2048", "--fp16", "--check", "--iters", "5"],
+                                  ["64", "5120", "2048", "--ex", "--check", "--iters", "5"]])
+def test_c_harness_runs_without_python_in_the_loop(args):
+    """cbench/bench_scaled_mm: a plain C process that links the library, launches through `launch_scaled_mm` (reference argument
+    order) or `feather_scaled_mm_ex`, times with events and checks sampled outputs against a host sum."""
+    import importlib.util
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("feather_b200_build", os.path.join(root, "comfyui-featherops_b200", "build.py"))
+    builder = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(builder)
+    binary = builder.CBENCH_BIN if os.path.exists(builder.CBENCH_BIN) else builder.build_cbench()
+    res = subprocess.run([binary, *args], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    print(res.stdout)
+    assert res.returncode == 0, res.stdout
+    assert "TFLOPS" in res.stdout and "-> ok" in res.stdout
