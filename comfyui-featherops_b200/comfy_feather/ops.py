@@ -3,9 +3,10 @@ prepacked fp8e5m2 and runs the sm_100a mixed-precision GEMM.
 
 Same surface and behaviour as the reference's comfy_feather/ops.py:17-148 (state-dict loading with `weight_scale` /
 legacy `scale_weight`, exclusion rules, `convert_weight` / `set_weight` for LoRA merging, un-merged LoRA patches),
-with one difference in `forward`: the reference pads the token count up to a multiple of 16/32/64/128 with `F.pad`
+with two differences in `forward`: the reference pads the token count up to a multiple of 16/32/64/128 with `F.pad`
 (ops.py:126-139) because its kernel needs tile-divisible M; the B200 kernel handles ragged M itself, so no padded copy
-is made and the rows beyond M never exist.
+is made and the rows beyond M never exist.  And the two dtype passes around the op (ops.py:88,103) are folded into the
+GEMM launch for fp16 / bf16 inputs.
 """
 
 import torch
@@ -14,7 +15,7 @@ from comfy.ops import cast_bias_weight, manual_cast, run_every_op, uncast_bias_w
 from torch import nn
 
 from ..kernel.convert import bf16_to_fp16
-from ..kernel.hip.hip_kernel import scaled_mm_hip
+from ..kernel.hip.hip_kernel import scaled_mm_b200
 from .lora import apply_lora_patches
 from .quant import get_feather_plain_tensors, is_feather_quantized_weight, make_feather_quantized_weight, quantize_feather_weight
 
@@ -80,15 +81,23 @@ def feather_ops(out_dtype=torch.bfloat16, excluded_names=()):
                 self.weight = nn.Parameter(weight, requires_grad=False)
 
             def _forward_quantized(self, x):
-                """x [M,K] any float dtype -> [M,N] in x's dtype, through the fp16 x e5m2 kernel."""
+                """x [M,K] any float dtype -> [M,N] in x's dtype, through the fp16/bf16 x e5m2 kernel.
+
+                The reference casts the activations to fp16, runs the op and casts the result back (ops.py:88,103).  Here
+                both casts happen inside the GEMM launch for 16-bit inputs: bf16 activations are multiplied as they are
+                (bitwise the cast-first result for every value fp16 represents exactly; values beyond +-65504, which the
+                cast would turn into inf, are multiplied unrounded), and the epilogue stores x's dtype after rounding to
+                `out_dtype` and adding the bias in `out_dtype`, exactly the two roundings of `op(...).to(dtype)`.
+                """
                 dtype_orig = x.dtype
                 x = x.contiguous()
-                if x.dtype == torch.bfloat16 and x.is_cuda:
-                    # the library's own cast kernel (kernel/convert.py:bf16_to_fp16 in the reference): same bits as
-                    # `x.to(torch.float16)`, measured 0.11 ms against 0.50 ms for 32768 x 5120 activations
+                if x.dtype == torch.bfloat16 and x.is_cuda and x.shape[0] <= 16:
+                    # a handful of tokens: the bandwidth-bound streaming kernel takes fp16, and the cast of M x K values is
+                    # nothing (the library's cast kernel, kernel/convert.py:bf16_to_fp16 in the reference: same bits as `x.to`)
                     x = bf16_to_fp16(x)
-                else:
+                elif x.dtype not in (torch.float16, torch.bfloat16):
                     x = x.to(torch.float16)
+                final_dtype = dtype_orig if dtype_orig in (torch.float16, torch.bfloat16) else self.out_dtype
 
                 # cast_bias_weight must not apply low-VRAM LoRA patches to the prepacked weight
                 saved_weight_function = self.weight_function
@@ -98,11 +107,11 @@ def feather_ops(out_dtype=torch.bfloat16, excluded_names=()):
                     weight, bias, offload_stream = cast_bias_weight(self, x, dtype=self.weight.dtype, bias_dtype=bias_dtype, offloadable=True)
                     qdata, scale = get_feather_plain_tensors(weight)
                     scale = scale.to(device=x.device, dtype=torch.float32)
-                    y = scaled_mm_hip(x, qdata, scale, bias, out_dtype=self.out_dtype)
+                    y = scaled_mm_b200(x, qdata, scale, bias, out_dtype=self.out_dtype, final_dtype=final_dtype)
                     uncast_bias_weight(self, weight, bias, offload_stream)
                 finally:
                     self.weight_function = saved_weight_function
-                return y.to(dtype_orig)
+                return y if y.dtype == dtype_orig else y.to(dtype_orig)
 
             def forward(self, input: torch.Tensor) -> torch.Tensor:
                 x = input

@@ -290,11 +290,12 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor for kind::f16: fp16 A and B, both K-major, fp32 accumulator.
-__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
-    return (1u << 4)           // D format: f32
-           | (0u << 7)         // A format: f16
-           | (0u << 10)        // B format: f16
+// Instruction descriptor for kind::f16: A and B both fp16 or both bf16 (the two formats cannot be mixed), both K-major,
+// fp32 accumulator.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n, bool bf16 = false) {
+    return (1u << 4)                      // D format: f32
+           | ((bf16 ? 1u : 0u) << 7)      // A format: f16 / bf16
+           | ((bf16 ? 1u : 0u) << 10)     // B format: f16 / bf16
            | (0u << 15)        // A K-major
            | (0u << 16)        // B K-major
            | ((n >> 3) << 17)  // N

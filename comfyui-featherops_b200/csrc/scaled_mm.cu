@@ -119,7 +119,11 @@ struct MmParams {
     long long* stats;   // optional [32] cycle counters written by CTA 0 (profiling aid), or null
     int M, N, K;
     long long ldc;
-    int out_bf16;
+    int out_bf16;  // dtype the scaled sum is rounded to and the bias is added in
+    int flip_final;  // 1: the value is then cast once more, to the other 16-bit dtype, and stored as that (the caller's `y.to(dtype)`)
+    int a_bf16;    // 1: the activations are bf16 (the weights are upcast to bf16 too, and the MMA runs bf16 x bf16)
+    int w_e4m3;    // 1: the weight bytes are fp8e4m3fn; they are upcast to 1/256 of their value and scale_mul puts the factor back
+    float scale_mul;
     int a3d;       // 1: the token tensor map is the 3-D form (64 k, M, K/64): one copy per k-block
     int c3d;       // 1: the output tensor maps are the 3-D form (64 n, M, N/64): one store per staged block and destination
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
@@ -193,16 +197,41 @@ __device__ __forceinline__ void give_up(const MmParams& p, volatile int* abort_f
     if (p.status != nullptr) atomicCAS(p.status, 0, FEATHER_ERR_DEVICE_TIMEOUT | (role << 8) | ((detail & 0xFFFF) << 16));
 }
 
-__device__ __forceinline__ uint16_t finish_value(float acc, float scale, bool out_bf16, bool has_bias, uint16_t bias_bits) {
+// flip: after rounding to the output dtype and adding the bias in it, cast once more to the other 16-bit dtype (what
+// `y.to(dtype)` does after the reference's op, comfy_feather/ops.py:103) and return those bits.
+__device__ __forceinline__ uint16_t finish_value(float acc, float scale, bool out_bf16, bool has_bias, uint16_t bias_bits, bool flip = false) {
     const float r = acc * scale;
     if (out_bf16) {
         __nv_bfloat16 v = __float2bfloat16_rn(r);
         if (has_bias) v = __float2bfloat16_rn(__bfloat162float(v) + __bfloat162float(__ushort_as_bfloat16(bias_bits)));
+        if (flip) return __half_as_ushort(__float2half_rn(__bfloat162float(v)));
         return __bfloat16_as_ushort(v);
     }
     __half v = __float2half_rn(r);
     if (has_bias) v = __hadd(v, __ushort_as_half(bias_bits));
+    if (flip) return __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(v)));
     return __half_as_ushort(v);
+}
+
+// One word of weight bytes as two fp16-positioned halves h = [b_hi : 0 : b_lo : 0] (what `byte << 8` gives) -> the two MMA
+// operand values.  mode bit 0: activations are bf16, so the operand must be bf16 too; bit 1: the bytes are e4m3fn.
+//   e5m2 -> fp16   h itself (exact: e5m2 is the high byte of an fp16)
+//   e4m3 -> fp16   sign | (b & 0x7F) << 7 is the value / 256 (exponent bias 7 read as 15; subnormals line up too), which the
+//                  epilogue undoes through scale_mul; the two NaN codes 0x7F / 0xFF are mapped to an fp16 NaN
+//   ... -> bf16    through fp32 (every fp16 value above is a bf16 value: at most 3 mantissa bits, exponent in range)
+__device__ __forceinline__ uint32_t upcast_pair(uint32_t h, int mode) {
+    if (mode & 2) {
+        const uint32_t mag = h & 0x7F007F00u;
+        uint32_t t = ((h >> 1) & 0x3F803F80u) | (h & 0x80008000u);
+        t |= __vcmpeq2(mag, 0x7F007F00u) & 0x7E007E00u;
+        h = t;
+    }
+    if (mode & 1) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+        h = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    return h;
 }
 
 // Two accumulator values of one output column (tokens j and j+1) -> packed out-dtype pair {lo = token j, hi = token j+1}:
@@ -400,7 +429,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (warp == kMmaWarp || (kIssuers == 2 && warp == kMma2Warp)) {
         // ------------------------------------------------------------------ MMA issuers (leader CTA, one lane per issuing warp)
         if (rank == 0 && lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_f16(kBW * CG, TN);
+            const uint32_t idesc = umma_idesc_f16(kBW * CG, TN, p.a_bf16 != 0);
             const uint32_t issuer = warp == kMmaWarp ? 0u : 1u;
             // One lane runs this loop (a loop that the whole warp runs in lockstep, with lane 0 issuing, measured slower: its
             // waits cost more).  It is written for instruction count: for tiles narrower than 256 tokens the tensor pipe
@@ -513,6 +542,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int g = (warp - kFirstTransformWarp) >> 2;
         const uint32_t w_lane_off = static_cast<uint32_t>(q * 32 + lane) * 16u;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
+        const int up_mode = (p.a_bf16 ? 1 : 0) | (p.w_e4m3 ? 2 : 0);
         // Running ring positions of the next k-block (weight-byte ring, operand ring) and whose turn it is; no division in the loop.
         uint32_t ws = 0, wph = 0, os = 0, oph = 0;
         int turn = 0;
@@ -557,16 +587,30 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                      : "=r"(x[j][0]), "=r"(x[j][1]), "=r"(x[j][2]), "=r"(x[j][3])
                                      : "r"(src + j * (kBW * 16)));
+                    if (up_mode == 0) {
 #pragma unroll
-                    for (int j = 0; j < kKSteps; ++j) {
-                        uint32_t v[8];
-                        // bytes b0..b3 of a word are k, k+1, k+2, k+3; fp16(b) = b << 8
+                        for (int j = 0; j < kKSteps; ++j) {
+                            uint32_t v[8];
+                            // bytes b0..b3 of a word are k, k+1, k+2, k+3; fp16(b) = b << 8
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            v[2 * i] = __byte_perm(x[j][i], 0u, 0x1404);
-                            v[2 * i + 1] = __byte_perm(x[j][i], 0u, 0x3424);
+                            for (int i = 0; i < 4; ++i) {
+                                v[2 * i] = __byte_perm(x[j][i], 0u, 0x1404);
+                                v[2 * i + 1] = __byte_perm(x[j][i], 0u, 0x3424);
+                            }
+                            tmem_st_32x32b_x8(dst + j * 8, v);
                         }
-                        tmem_st_32x32b_x8(dst + j * 8, v);
+                    } else {
+                        // bf16 activations and / or e4m3 weights: a few more integer / convert instructions per pair
+#pragma unroll
+                        for (int j = 0; j < kKSteps; ++j) {
+                            uint32_t v[8];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                v[2 * i] = upcast_pair(__byte_perm(x[j][i], 0u, 0x1404), up_mode);
+                                v[2 * i + 1] = upcast_pair(__byte_perm(x[j][i], 0u, 0x3424), up_mode);
+                            }
+                            tmem_st_32x32b_x8(dst + j * 8, v);
+                        }
                     }
                 }
                 tc_wait_st();
@@ -595,8 +639,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int grp = warp >> 2;
         const bool group_leader = (threadIdx.x & 127) == 0;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
-        const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+        const float scale = (p.scale != nullptr ? __ldg(p.scale) : 1.0f) * p.scale_mul;
         const bool out_bf16 = p.out_bf16 != 0;
+        const bool flip = p.flip_final != 0;
         const bool has_bias = p.bias != nullptr;
         uint16_t* const c16 = reinterpret_cast<uint16_t*>(p.c);
         constexpr int kTileCols = kBW * CG;
@@ -688,18 +733,29 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 // thread t supplies the address of row t % 8 of matrix t / 8
                 const uint32_t st_lane = (q >> 1) * (kOutRows * 128) + (lane & 7) * 128 +
                                          (((static_cast<uint32_t>(q & 1) * 4 + (lane >> 3)) ^ (lane & 7)) << 4);
-                auto drain = [&](auto bf16_tag, auto bias_tag) {
+                auto drain = [&](auto bf16_tag, auto bias_tag, auto flip_tag) {
                     constexpr bool kBf16 = decltype(bf16_tag)::value;
                     constexpr bool kBias = decltype(bias_tag)::value;
+                    constexpr bool kFlip = decltype(flip_tag)::value;     // store the other 16-bit dtype (one more rounding)
                     auto pack = [&](uint32_t x0, uint32_t x1, uint32_t b2) -> uint32_t {
                         const float r0 = __uint_as_float(x0) * scale, r1 = __uint_as_float(x1) * scale;
                         if constexpr (kBf16) {
                             __nv_bfloat162 x = __floats2bfloat162_rn(r0, r1);
                             if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __nv_bfloat162*>(&b2));
+                            if constexpr (kFlip) {
+                                const float2 f = __bfloat1622float2(x);
+                                const __half2 y = __floats2half2_rn(f.x, f.y);
+                                return *reinterpret_cast<const uint32_t*>(&y);
+                            }
                             return *reinterpret_cast<const uint32_t*>(&x);
                         } else {
                             __half2 x = __floats2half2_rn(r0, r1);
                             if constexpr (kBias) x = __hadd2(x, *reinterpret_cast<const __half2*>(&b2));
+                            if constexpr (kFlip) {
+                                const float2 f = __half22float2(x);
+                                const __nv_bfloat162 y = __floats2bfloat162_rn(f.x, f.y);
+                                return *reinterpret_cast<const uint32_t*>(&y);
+                            }
                             return *reinterpret_cast<const uint32_t*>(&x);
                         }
                     };
@@ -805,12 +861,16 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 };
                 tw.start();
                 if (alive) {
+                    auto with_flip = [&](auto bf16_tag, auto bias_tag) {
+                        if (flip) drain(bf16_tag, bias_tag, std::true_type{});
+                        else drain(bf16_tag, bias_tag, std::false_type{});
+                    };
                     if (out_bf16) {
-                        if (has_bias) drain(std::true_type{}, std::true_type{});
-                        else drain(std::true_type{}, std::false_type{});
+                        if (has_bias) with_flip(std::true_type{}, std::true_type{});
+                        else with_flip(std::true_type{}, std::false_type{});
                     } else {
-                        if (has_bias) drain(std::false_type{}, std::true_type{});
-                        else drain(std::false_type{}, std::false_type{});
+                        if (has_bias) with_flip(std::false_type{}, std::true_type{});
+                        else with_flip(std::false_type{}, std::false_type{});
                     }
                 } else {
                     // bystander: joins the group's two barriers per block and nothing else
@@ -838,7 +898,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 if (c0 + j < valid)
-                                    c_col[static_cast<long long>(c0 + j) * p.ldc] = finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits);
+                                    c_col[static_cast<long long>(c0 + j) * p.ldc] = finish_value(__uint_as_float(v[j]), scale, out_bf16, has_bias, bias_bits, flip);
                             }
                         }
                     }
@@ -890,7 +950,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
                                 if (c0 + i < valid)
-                                    c16[static_cast<long long>(w.tok0 + c0 + i) * p.ldc + n] = finish_value(acc[i], scale, out_bf16, has_bias, bias_bits);
+                                    c16[static_cast<long long>(w.tok0 + c0 + i) * p.ldc + n] = finish_value(acc[i], scale, out_bf16, has_bias, bias_bits, flip);
                         }
                     }
                 }
@@ -1134,7 +1194,14 @@ static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMa
 }
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                   int output_dtype, int sms, cudaStream_t stream);   // small_m.cu
+                   int output_dtype, int flip_final, int sms, cudaStream_t stream);   // small_m.cu
+
+// Operand and result types beyond the reference's fp16 x e5m2 -> out dtype.
+struct Types {
+    bool a_bf16 = false;     // activations are bf16
+    bool w_e4m3 = false;     // weights are fp8e4m3fn
+    int final_dtype = -1;    // dtype stored (FEATHER_OUT_*); -1: the output dtype itself
+};
 
 // Bandwidth-bound end (at most 16 tokens, or on request): the register-streaming kernel, unless the caller pinned a
 // tensor-memory variant or the output goes to several buffers.  split_k = 1 only says "no workspace" (the reference-ABI
@@ -1148,7 +1215,7 @@ static bool takes_streaming_kernel(const feather_mm_variant* variant, int64_t M,
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
                           int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant, void* workspace,
                           size_t workspace_bytes, int* status_dev, cudaStream_t stream, void* const* extra_dst = nullptr, int n_extra = 0,
-                          int64_t scatter_rows = 0) {
+                          int64_t scatter_rows = 0, Types types = Types()) {
     if (a == nullptr || b == nullptr || c == nullptr) return set_error(FEATHER_ERR_BAD_ARGUMENT, "a, b_prepacked and c must not be null");
     if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
     if (K % 16 != 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "K must be divisible by 16");
@@ -1174,9 +1241,15 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     for (int d = 0; d < n_extra; ++d)
         if (extra_dst == nullptr || extra_dst[d] == nullptr || (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15u) != 0)
             return set_error(FEATHER_ERR_BAD_ARGUMENT, "every output buffer must be non-null and 16-byte aligned");
-    if (takes_streaming_kernel(variant, M, n_extra))
-        return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, sms, stream);
-    if (which == FEATHER_KERNEL_STREAM) return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer");
+    if (types.final_dtype != -1 && types.final_dtype != FEATHER_OUT_FP16 && types.final_dtype != FEATHER_OUT_BF16)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "final_dtype must be -1 (same as output_dtype), 0 (fp16) or 1 (bf16)");
+    const int flip_final = (types.final_dtype != -1 && types.final_dtype != output_dtype) ? 1 : 0;
+    // the streaming kernel multiplies fp16 activations by e5m2 weights only; the other operand types take the tensor-memory kernel
+    const bool plain_operands = !types.a_bf16 && !types.w_e4m3;
+    if (plain_operands && takes_streaming_kernel(variant, M, n_extra))
+        return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, flip_final, sms, stream);
+    if (which == FEATHER_KERNEL_STREAM)
+        return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer and takes fp16 activations and e5m2 weights");
     Plan pl;
     if (!make_plan(M, N, K, variant, workspace ? workspace_bytes : 0, true, sms, &pl))
         return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
@@ -1266,6 +1339,10 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.K = static_cast<int>(K);
     p.ldc = ldc;
     p.out_bf16 = output_dtype == FEATHER_OUT_BF16 ? 1 : 0;
+    p.flip_final = flip_final;
+    p.a_bf16 = types.a_bf16 ? 1 : 0;
+    p.w_e4m3 = types.w_e4m3 ? 1 : 0;
+    p.scale_mul = types.w_e4m3 ? 256.0f : 1.0f;
     // Read once per process.
     static const bool env_stats = getenv("FEATHER_STATS") != nullptr;
     // FEATHER_STATS=1: the caller's status buffer is at least 8 + 32*8 bytes and receives the cycle counters of CTA 0 after the status word
@@ -1308,6 +1385,22 @@ extern "C" int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, c
                           static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_t* b_prepacked, int b_dtype, const float* scale, const void* bias, void* c,
+                                       int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, int final_dtype,
+                                       const feather_mm_variant* variant, void* workspace, size_t workspace_bytes, int* status_dev,
+                                       feather_stream_t stream) {
+    if (a_dtype != FEATHER_SRC_FP16 && a_dtype != FEATHER_SRC_BF16)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "a_dtype must be %d (bf16) or %d (fp16)", FEATHER_SRC_BF16, FEATHER_SRC_FP16);
+    if (b_dtype != FEATHER_B_E5M2 && b_dtype != FEATHER_B_E4M3)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "b_dtype must be %d (fp8e4m3fn) or %d (fp8e5m2)", FEATHER_B_E4M3, FEATHER_B_E5M2);
+    Types t;
+    t.a_bf16 = a_dtype == FEATHER_SRC_BF16;
+    t.w_e4m3 = b_dtype == FEATHER_B_E4M3;
+    t.final_dtype = final_dtype;
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, workspace, workspace_bytes, status_dev,
+                          static_cast<cudaStream_t>(stream), nullptr, 0, 0, t);
+}
+
 extern "C" int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* const* c_list_host,
                                        int n_dst, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
                                        int* status_dev, feather_stream_t stream) {
@@ -1336,14 +1429,16 @@ extern "C" int feather_scaled_mm_scatter(const void* a, const uint8_t* b_prepack
 extern "C" int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
                                 int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, int, int, int, int, int, int b_dtype,
                                 int output_dtype, feather_stream_t stream) {
-    if (b_dtype != FEATHER_B_E5M2) {
-        set_error(FEATHER_ERR_UNSUPPORTED, "only fp8e5m2 weights (b_dtype = 1) are supported");
+    if (b_dtype != FEATHER_B_E5M2 && b_dtype != FEATHER_B_E4M3) {
+        set_error(FEATHER_ERR_UNSUPPORTED, "b_dtype must be 0 (fp8e4m3fn) or 1 (fp8e5m2)");
         return 0;
     }
     feather_mm_variant v{};
     v.split_k = 1;   // no workspace through this signature
+    Types t;
+    t.w_e4m3 = b_dtype == FEATHER_B_E4M3;
     const int st = scaled_mm_impl(a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K, N, output_dtype, &v,
-                                  nullptr, 0, nullptr, static_cast<cudaStream_t>(stream));
+                                  nullptr, 0, nullptr, static_cast<cudaStream_t>(stream), nullptr, 0, 0, t);
     return st == FEATHER_OK ? 1 : 0;
 }
 

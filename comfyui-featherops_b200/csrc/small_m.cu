@@ -35,15 +35,19 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint16_t sm_finish(float acc, float scale, bool out_bf16, bool has_bias, uint16_t bias_bits) {
+// out_mode bit 0: the scaled sum is rounded to bf16 (else fp16) and the bias is added in that dtype; bit 1: the value is then
+// cast once more, to the other 16-bit dtype, and stored as that.
+__device__ __forceinline__ uint16_t sm_finish(float acc, float scale, int out_mode, bool has_bias, uint16_t bias_bits) {
     const float r = acc * scale;
-    if (out_bf16) {
+    if (out_mode & 1) {
         __nv_bfloat16 v = __float2bfloat16_rn(r);
         if (has_bias) v = __float2bfloat16_rn(__bfloat162float(v) + __bfloat162float(__ushort_as_bfloat16(bias_bits)));
+        if (out_mode & 2) return __half_as_ushort(__float2half_rn(__bfloat162float(v)));
         return __bfloat16_as_ushort(v);
     }
     __half v = __float2half_rn(r);
     if (has_bias) v = __hadd(v, __ushort_as_half(bias_bits));
+    if (out_mode & 2) return __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(v)));
     return __half_as_ushort(v);
 }
 
@@ -152,7 +156,7 @@ small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, co
 #pragma unroll
                 for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (kTok * kPitch) + tok * kPitch + col];   // warp order: deterministic
                 const uint16_t bias_bits = has_bias ? __ldg(bias + n) : uint16_t(0);
-                c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16 != 0, has_bias, bias_bits);
+                c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16, has_bias, bias_bits);
             }
         }
         __syncthreads();
@@ -245,7 +249,7 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
 #pragma unroll
                 for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (8 * kPitch) + tok * kPitch + col];
                 const uint16_t bias_bits = has_bias ? __ldg(bias + n) : uint16_t(0);
-                c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16 != 0, has_bias, bias_bits);
+                c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16, has_bias, bias_bits);
             }
         }
         __syncthreads();
@@ -328,8 +332,9 @@ static int pick_strips(int N, int sms, int max_p, int strip_cols = 8) {
     case P_: e = launch_small8<P_, U_>(a, w, scale, bias, c, m, n, k, ldc, out_bf16, sms, stream); break;
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                   int output_dtype, int sms, cudaStream_t stream) {
-    const int out_bf16 = output_dtype == FEATHER_OUT_BF16 ? 1 : 0;
+                   int output_dtype, int flip_final, int sms, cudaStream_t stream) {
+    // the kernels' `out_bf16` argument carries both bits of sm_finish's out_mode
+    const int out_bf16 = (output_dtype == FEATHER_OUT_BF16 ? 1 : 0) | (flip_final ? 2 : 0);
     const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
     cudaError_t e = cudaErrorInvalidValue;
     if (M <= 8) {

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_workspace_bytes",
     "feather_scaled_mm_choose",
     "feather_scaled_mm_static",
+    "feather_scaled_mm_typed",
     "feather_scaled_mm_multi",
     "feather_scaled_mm_scatter",
     "feather_reduce_partials",
@@ -97,6 +98,8 @@ def load_library():
         lib.feather_scaled_mm_static.restype = ci
         lib.feather_scaled_mm_multi.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
         lib.feather_scaled_mm_multi.restype = ci
+        lib.feather_scaled_mm_typed.argtypes = [vp, ci, vp, ci, vp, vp, vp, i64, i64, i64, i64, ci, ci, ctypes.POINTER(MMVariant), vp, sz, vp, vp]
+        lib.feather_scaled_mm_typed.restype = ci
         lib.feather_scaled_mm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
         lib.feather_scaled_mm_scatter.restype = ci
         lib.feather_reduce_partials.argtypes = [vp, ci, i64, i64, vp, vp, i64, ctypes.POINTER(vp), ci, i64, ci, vp]
@@ -352,6 +355,36 @@ def scaled_mm_into(a, b_prepacked, scale, bias, c, variant=None, n_cols=None):
         )
     if status != FEATHER_OK:
         _check(status, "feather_scaled_mm_ex")
+    return c
+
+
+B_E4M3, B_E5M2 = 0, 1
+_B_CODE = {torch.float8_e4m3fn: B_E4M3, torch.float8_e5m2: B_E5M2}
+
+
+def scaled_mm_typed_into(a, b_prepacked, scale, bias, c, out_dtype=None, variant=None):
+    """c = cast_to_c_dtype(cvt_out_dtype((a @ up(b)) * scale) + bias) through `feather_scaled_mm_typed`.
+
+    a: fp16 or bf16 (bf16 is multiplied as it is, no cast pass); b_prepacked: float8_e5m2 or float8_e4m3fn [K/16, N, 16];
+    out_dtype: dtype of the rounding and of the bias (default: c's); c may have the other 16-bit dtype, which costs one more
+    rounding in the epilogue instead of a separate `y.to(dtype)` pass.
+    """
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, c)
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    out_dtype = c.dtype if out_dtype is None else out_dtype
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    stream = _raw_stream(index)
+    index, ws_ptr, ws_bytes, st_ptr = _scratch_ptrs_for(dev, stream)
+    with _OnDevice(index):
+        status = lib.feather_scaled_mm_typed(
+            a.data_ptr(), _SRC_CODE[a.dtype], b_prepacked.data_ptr(), _B_CODE[b_prepacked.dtype], _addr(scale), _addr(bias), c.data_ptr(),
+            M, N, K, c.stride(0), _OUT_CODE[out_dtype], _OUT_CODE[c.dtype],
+            ctypes.byref(variant) if variant is not None else None, ws_ptr, ws_bytes, st_ptr, stream,
+        )
+    if status != FEATHER_OK:
+        _check(status, "feather_scaled_mm_typed")
     return c
 
 

@@ -8,9 +8,16 @@ scripts import it unchanged), routed to the sm_100a library instead of the HIP e
     prepack_b_for_scaled_mm(b)                                                 hip_kernel.py:170-171
     torch.ops.feather_ops.scaled_mm(a, b, scale, bias, c, 5 ints, b_dtype)     hip_kernel.cu:746-767
 
+    torch.ops.feather_ops_internal.scaled_mm_autotuned(...)                    hip_kernel.py:95-133 (the op torch.compile sees)
+
 Differences a caller can observe: the five tile integers are accepted and ignored (the kernel variant is chosen from
-the shape, so there is no first-call autotune pause); M does not have to be a multiple of any tile (ragged token counts
-are handled in the kernel); fp8e4m3 weights are rejected.
+the shape, so there is no first-call autotune pause and nothing for inductor to tune); M does not have to be a multiple of
+any tile (ragged token counts are handled in the kernel); fp8e4m3fn weights are upcast exactly (subnormals and NaN codes
+included; the reference's kernel approximates them, hip_kernel.cu:83-99).
+
+One addition: `scaled_mm_b200(a, b_prepacked, scale, bias, out_dtype, final_dtype)` takes bf16 activations as they are
+and can store the other 16-bit dtype, which removes the two elementwise passes the reference's `FeatherOps.Linear.forward`
+runs around the GEMM (comfy_feather/ops.py:88,103).
 """
 
 import torch
@@ -35,7 +42,7 @@ def _check(cond, msg):
         raise RuntimeError(msg)
 
 
-def _validate(a, b_prepacked, scale, bias, c, b_dtype):
+def _validate(a, b_prepacked, scale, bias, c, b_dtype, allow_bf16_a=False, bias_dtype=None):
     """Argument checks of the reference op (hip_kernel.cu:648-730), minus tile divisibility of M and N.
 
     Written as plain `if` statements so that a message is only formatted when its check fails: this runs on every call and
@@ -50,16 +57,16 @@ def _validate(a, b_prepacked, scale, bias, c, b_dtype):
         raise RuntimeError("b_prepacked must be on the same device as a")
     if not (c.device == a.device):
         raise RuntimeError("c must be on the same device as a")
-    if not (a.dtype == torch.float16):
+    if not (a.dtype == torch.float16 or (allow_bf16_a and a.dtype == torch.bfloat16)):
         raise RuntimeError("a must be float16")
     if not (c.dtype in (torch.float16, torch.bfloat16)):
         raise RuntimeError("c must be float16 or bfloat16")
     if not (b_dtype in (0, 1)):
         raise RuntimeError("b_dtype must be 0 (fp8e4m3) or 1 (fp8e5m2)")
-    if not (b_dtype == 1):
-        raise RuntimeError("fp8e4m3 weights are not supported by the sm_100a kernel; b_dtype must be 1 (fp8e5m2)")
-    if not (b_prepacked.dtype == torch.float8_e5m2):
+    if b_dtype == 1 and not (b_prepacked.dtype == torch.float8_e5m2):
         raise RuntimeError("b_prepacked must be float8_e5m2 when b_dtype=1")
+    if b_dtype == 0 and not (b_prepacked.dtype == torch.float8_e4m3fn):
+        raise RuntimeError("b_prepacked must be float8_e4m3fn when b_dtype=0")
     if not (a.dim() == 2):
         raise RuntimeError("a must be 2D")
     if not (b_prepacked.dim() == 3):
@@ -106,8 +113,8 @@ def _validate(a, b_prepacked, scale, bias, c, b_dtype):
             raise RuntimeError("bias must be a CUDA tensor")
         if not (bias.device == a.device):
             raise RuntimeError("bias must be on the same device as a")
-        if not (bias.dtype == c.dtype):
-            raise RuntimeError("bias must have the same dtype as c")
+        if not (bias.dtype == (c.dtype if bias_dtype is None else bias_dtype)):
+            raise RuntimeError("bias must have the same dtype as c" if bias_dtype is None else "bias must have the out dtype")
         if not (bias.numel() == N):
             raise RuntimeError("bias must have N elements")
         if not (bias.is_contiguous()):
@@ -132,7 +139,10 @@ def _scaled_mm_cuda(a, b_prepacked, scale, bias, c, block_warps_m, block_warps_n
     _validate(a, b_prepacked, scale, bias, c, b_dtype)
     if a.shape[0] == 0:
         return
-    native.scaled_mm_into(a, b_prepacked, scale, bias, c)
+    if b_dtype == 1:
+        native.scaled_mm_into(a, b_prepacked, scale, bias, c)
+    else:
+        native.scaled_mm_typed_into(a, b_prepacked, scale, bias, c)
 
 
 _lib_impl = torch.library.Library("feather_ops", "IMPL")
@@ -174,6 +184,71 @@ def _(a, b_prepacked, scale, bias, out_dtype, block_warps_m, block_warps_n, unro
 
 scaled_mm_hip_configured = _configured_op
 
+
+# The op the reference hands to torch.compile (hip_kernel.py:95-133): scale and bias always tensors plus two flags, the five
+# tile integers optional.  The reference registers it with inductor's custom-op autotuning over its 28 tile configs; here
+# the variant follows from the shape inside the library, so there is nothing to tune and the op forwards to the configured
+# op.  Kept so graphs and scripts that name `feather_ops_internal::scaled_mm_autotuned` keep working.
+@torch.library.custom_op("feather_ops_internal::scaled_mm_autotuned", mutates_args=())
+def _autotuned_op(
+    a: torch.Tensor,
+    b_prepacked: torch.Tensor,
+    scale: torch.Tensor,
+    bias: torch.Tensor,
+    out_dtype: torch.dtype,
+    has_scale: bool,
+    has_bias: bool,
+    block_warps_m: int = 0,
+    block_warps_n: int = 0,
+    unroll_k: int = 0,
+    repeat_m: int = 0,
+    repeat_n: int = 0,
+) -> torch.Tensor:
+    return _configured_op(a, b_prepacked, scale if has_scale else None, bias if has_bias else None, out_dtype, *_DEFAULT_CFG)
+
+
+@_autotuned_op.register_fake
+def _(a, b_prepacked, scale, bias, out_dtype, has_scale, has_bias, block_warps_m=0, block_warps_n=0, unroll_k=0, repeat_m=0, repeat_n=0):
+    return torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
+
+
+# bf16 or fp16 activations in, either 16-bit dtype out: one launch, no elementwise pass before or after it.
+def _typed_impl(a, b_prepacked, scale, bias, out_dtype, final_dtype):
+    if final_dtype not in (torch.float16, torch.bfloat16) or out_dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("out_dtype and final_dtype must be float16 or bfloat16")
+    out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=final_dtype)
+    _validate(a, b_prepacked, scale, bias, out, 0 if b_prepacked.dtype == torch.float8_e4m3fn else 1, allow_bf16_a=True, bias_dtype=out_dtype)
+    if a.shape[0] != 0:
+        native.scaled_mm_typed_into(a, b_prepacked, scale, bias, out, out_dtype=out_dtype)
+    return out
+
+
+@torch.library.custom_op("feather_ops_internal::scaled_mm_b200", mutates_args=())
+def _typed_op(
+    a: torch.Tensor,
+    b_prepacked: torch.Tensor,
+    scale: torch.Tensor | None,
+    bias: torch.Tensor | None,
+    out_dtype: torch.dtype,
+    final_dtype: torch.dtype,
+) -> torch.Tensor:
+    return _typed_impl(a, b_prepacked, scale, bias, out_dtype, final_dtype)
+
+
+@_typed_op.register_fake
+def _(a, b_prepacked, scale, bias, out_dtype, final_dtype):
+    return torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=final_dtype)
+
+
+def scaled_mm_b200(a, b_prepacked, scale, bias, out_dtype, final_dtype=None):
+    """`scaled_mm_hip` with the casts around it folded in: `a` may be bf16 (multiplied as it is; equals casting it to fp16
+    first for every value fp16 represents exactly), and the result is stored as `final_dtype` (default `out_dtype`) after
+    the rounding to `out_dtype` and the bias add in `out_dtype` - the bits `scaled_mm_hip(...).to(final_dtype)` gives."""
+    final_dtype = out_dtype if final_dtype is None else final_dtype
+    if torch.compiler.is_compiling():
+        return _typed_op(a, b_prepacked, scale, bias, out_dtype, final_dtype)
+    return _typed_impl(a, b_prepacked, scale, bias, out_dtype, final_dtype)
+
 _DEFAULT_CFG = (1, 8, 4, 8, 2)
 
 
@@ -190,7 +265,9 @@ def scaled_mm_hip(
     in eager mode it validates, allocates the output and launches, with no autotune step.
     """
     if torch.compiler.is_compiling():
-        return _configured_op(a, b_prepacked, scale, bias, out_dtype, *_DEFAULT_CFG)
+        # the op name the reference's compiled graphs carry (hip_kernel.py:143-152)
+        return _autotuned_op(a, b_prepacked, scale if scale is not None else a, bias if bias is not None else a, out_dtype,
+                             scale is not None, bias is not None)
     out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
     _scaled_mm_cuda(a, b_prepacked, scale, bias, out, *_DEFAULT_CFG, 0 if b_prepacked.dtype == torch.float8_e4m3fn else 1)
     return out

@@ -39,7 +39,7 @@ typedef void* feather_stream_t;
 typedef enum feather_status {
     FEATHER_OK = 0,
     FEATHER_ERR_BAD_ARGUMENT = 1,    /* null pointer, negative size, K % 16 != 0, misaligned pointer ... */
-    FEATHER_ERR_UNSUPPORTED = 2,     /* e.g. b_dtype = fp8e4m3, unknown kernel variant */
+    FEATHER_ERR_UNSUPPORTED = 2,     /* e.g. unknown kernel variant, streaming kernel asked for more than 32 tokens */
     FEATHER_ERR_WORKSPACE = 3,       /* variant needs more scratch than was passed */
     FEATHER_ERR_CUDA = 4,            /* a CUDA runtime / driver call failed; see feather_last_error_string */
     FEATHER_ERR_DEVICE_TIMEOUT = 5,  /* value found in *status_dev after a kernel gave up on a bounded wait */
@@ -80,7 +80,7 @@ typedef struct feather_mm_variant {
 
 /* Drop-in for `extern "C" bool launch_scaled_mm(...)`, kernel/hip/hip_kernel.cu:564-582: same argument
  * order and meaning, cudaStream_t in place of hipStream_t.  The five tile integers are accepted and
- * ignored (the variant is chosen from the shape); b_dtype must be 1 (e5m2).  Returns 1 when the launch
+ * ignored (the variant is chosen from the shape); b_dtype is 1 (e5m2) or 0 (e4m3fn, upcast exactly).  Returns 1 when the launch
  * was enqueued, 0 otherwise (the reference returns false for an unknown config).  This entry point
  * takes no workspace, so it never splits K through one: up to 16 tokens it runs the register-streaming kernel (which
  * splits K inside a CTA), above that the tensor-memory kernel unsplit. */
@@ -104,6 +104,24 @@ FEATHER_API int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, cons
 FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c, int64_t M,
                          int64_t N, int64_t K, int64_t ldc, int output_dtype, const feather_mm_variant* variant,
                          void* workspace, size_t workspace_bytes, int* status_dev, feather_stream_t stream);
+
+/* The GEMM with the operand and result types the hot path meets around the reference's fp16 x e5m2 -> out-dtype core:
+ *   a_dtype      FEATHER_SRC_FP16 or FEATHER_SRC_BF16.  bf16 activations are multiplied as they are (the weights are upcast to
+ *                bf16, which holds every fp8 value exactly), so the caller's `x.to(fp16)` pass (comfy_feather/ops.py:88,
+ *                kernel/convert.py:24-34) disappears.  For every activation that fp16 represents exactly the result is bitwise
+ *                what cast-first gives; outside that range (|x| > 65504, or below 2^-14 with more bits than fp16 subnormals
+ *                keep) this path multiplies the unrounded value where cast-first would multiply inf or a rounded one.
+ *   b_dtype      FEATHER_B_E5M2 or FEATHER_B_E4M3 (fp8e4m3fn bytes in the same (K/16, N, 16) layout; exact upcast including
+ *                subnormals and the NaN codes - kernel/hip/hip_kernel.cu:83-99 of the reference approximates it).
+ *   output_dtype dtype the scaled sum is rounded to and the bias is added in (bias has this dtype), as in feather_scaled_mm_ex
+ *   final_dtype  dtype of c: -1 or output_dtype stores that value; the other 16-bit dtype applies one more rounding first,
+ *                which is the caller's `y.to(dtype_orig)` (comfy_feather/ops.py:103) done in the epilogue.
+ * Everything else as feather_scaled_mm_ex.  Up to 16 tokens of fp16 activations with e5m2 weights take the streaming kernel as
+ * there; bf16 activations and e4m3 weights always take the tensor-memory kernel. */
+FEATHER_API int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_t* b_prepacked, int b_dtype, const float* scale, const void* bias,
+                                        void* c, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, int final_dtype,
+                                        const feather_mm_variant* variant, void* workspace, size_t workspace_bytes, int* status_dev,
+                                        feather_stream_t stream);
 
 /* Column-sharded linear over the GPUs of one box, exchange fused into the GEMM: the same launch as feather_scaled_mm_ex,
  * but every finished output block is stored (TMA store) to each of the n_dst buffers in c_list_host - a HOST array of device

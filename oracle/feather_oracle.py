@@ -44,6 +44,17 @@ def e5m2_bits_to_f32(bits):
     return (b.astype(np.uint16) << np.uint16(8)).view(np.float16).astype(np.float32)
 
 
+def e4m3_bits_to_f32(bits):
+    """uint8 fp8e4m3fn patterns -> float32 (exact).  Sign, 4 exponent bits (bias 7), 3 mantissa bits; exponent field 0 is
+    subnormal (m * 2^-9); 0x7F / 0xFF are NaN and there is no infinity.  This is `b.to(torch.float16)` of naive.py:22 for a
+    float8_e4m3fn weight (the reference's kernel approximates it, hip_kernel.cu:83-99; naive.py is exact)."""
+    b = np.asarray(bits, dtype=np.uint8).astype(np.int32)
+    e, m = (b >> 3) & 0xF, b & 0x7
+    mag = np.where(e == 0, m * 2.0 ** -9, (1.0 + m / 8.0) * np.exp2((e - 7).astype(np.float64)))
+    mag = np.where((b & 0x7F) == 0x7F, np.nan, mag)
+    return np.where(b & 0x80, -mag, mag).astype(np.float32)
+
+
 def f32_to_e5m2_bits(x):
     """float32 -> e5m2 bit patterns: round-to-nearest-even, overflow to inf (no saturation), NaN -> sign|0x7F.
 
@@ -187,23 +198,35 @@ def layout_dequantize(qdata, scale, orig_dtype):
 # ------------------------------------------------------------------------------------------------
 # GEMM  (naive.py:4-41)
 # ------------------------------------------------------------------------------------------------
-def scaled_mm(a, b_prepacked, scale, bias, out_dtype, product="fp32"):
+def scaled_mm(a, b_prepacked, scale, bias, out_dtype, product="fp32", b_format="e5m2", a_format="fp16", final_dtype=None):
     """out = cvt((a @ up(b)) * scale) + bias, the math of kernel/naive.py:13-41 with b_prepacked=True.
 
-    a            float16 (M,K)
-    b_prepacked  uint8 e5m2 bits (K/16, N, 16)
+    a            float16 (M,K); with a_format='bf16' uint16 bf16 patterns that are multiplied as they are (the typed entry
+                 point's semantics; naive.py:21 would cast them to fp16 first, which `a_format='bf16_cast_first'` does)
+    b_prepacked  uint8 weight bits (K/16, N, 16), e5m2 or (b_format='e4m3') fp8e4m3fn
     scale        float or None;  bias: storage array of out_dtype, shape (N,), or None
     out_dtype    'fp16' | 'bf16'
     product      'fp32': the product keeps fp32 precision before `* scale` (what a fp32-accumulating kernel computes;
                          evaluated here in float64 and rounded once to fp32);
                  'fp16': the product is rounded to fp16 first, as naive.py:20-23 does verbatim (it overflows to inf
                          once |a @ b| exceeds 65504, which happens at amax/57344 scales).
-    Returns the storage array of out_dtype, shape (M,N).
+    final_dtype  None, or the 16-bit dtype the result is cast to afterwards (`y.to(dtype)`, comfy_feather/ops.py:103)
+    Returns the storage array of final_dtype or out_dtype, shape (M,N).
     """
     kb, n, _ = b_prepacked.shape
-    w = e5m2_bits_to_f32(b_prepacked.transpose(0, 2, 1).reshape(kb * 16, n))      # naive.py:13-16
+    w_bits = b_prepacked.transpose(0, 2, 1).reshape(kb * 16, n)                    # naive.py:13-16
+    w = e5m2_bits_to_f32(w_bits) if b_format == "e5m2" else e4m3_bits_to_f32(w_bits)
+    if a_format == "fp16":
+        a64 = np.asarray(a, dtype=np.float16).astype(np.float64)
+    elif a_format == "bf16":
+        a64 = bf16_bits_to_f32(a).astype(np.float64)
+    elif a_format == "bf16_cast_first":
+        with np.errstate(over="ignore"):
+            a64 = bf16_bits_to_f32(a).astype(np.float16).astype(np.float64)          # naive.py:21
+    else:
+        raise ValueError(a_format)
     with np.errstate(invalid="ignore", over="ignore"):
-        acc = (np.asarray(a, dtype=np.float16).astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
+        acc = (a64 @ w.astype(np.float64)).astype(np.float32)
         if product == "fp16":
             acc = acc.astype(np.float16).astype(np.float32)                       # naive.py:20-23
         elif product != "fp32":
@@ -213,6 +236,8 @@ def scaled_mm(a, b_prepacked, scale, bias, out_dtype, product="fp32"):
         out = round_to(acc, out_dtype)                                            # naive.py:34
         if bias is not None:
             out = round_to(out + to_f32(bias, out_dtype)[None, :], out_dtype)     # naive.py:35-40
+        if final_dtype is not None and final_dtype != out_dtype:
+            return from_f32(round_to(out, final_dtype), final_dtype)
     return from_f32(out, out_dtype)
 
 
@@ -233,12 +258,18 @@ def ulp_distance_16(x_bits, y_bits):
     return np.abs(key(x_bits) - key(y_bits))
 
 
-def error_report(out, ref, out_dtype):
-    """max|err|, rms(ref), Frobenius-relative error and max ulp distance between two outputs of `out_dtype`."""
+def error_report(out, ref, out_dtype, bias=None):
+    """max|err|, rms(ref), Frobenius-relative error and max ulp distance between two outputs of `out_dtype`.
+
+    `bias` (the [N] bias that was added, as float32 values): the output is cvt(acc * scale) + bias with the rounding BEFORE
+    the bias add (naive.py:34-40), so a one-ulp rounding-boundary flip has the size of an ulp of the pre-bias value, which can
+    be twice the ulp of the final value when the add crosses a binade downwards.  With `bias` given, "one ulp" is taken at
+    the larger of the two magnitudes."""
     o = to_f32(out, out_dtype).astype(np.float64)
     r = to_f32(ref, out_dtype).astype(np.float64)
     finite = np.isfinite(r) & np.isfinite(o)
-    same_nonfinite = np.array_equal(np.isnan(r), np.isnan(o)) and np.array_equal(np.isinf(r) * np.sign(r), np.isinf(o) * np.sign(o))
+    with np.errstate(invalid="ignore"):
+        same_nonfinite = np.array_equal(np.isnan(r), np.isnan(o)) and np.array_equal(np.where(np.isinf(r), np.sign(r), 0.0), np.where(np.isinf(o), np.sign(o), 0.0))
     with np.errstate(invalid="ignore"):
         d = np.where(finite, o - r, 0.0)
     rms = float(np.sqrt(np.mean(np.where(finite, r, 0.0) ** 2)))
@@ -250,7 +281,10 @@ def error_report(out, ref, out_dtype):
     # round a value sitting on a rounding boundary to different neighbours)
     mant = 10 if out_dtype == "fp16" else 7
     with np.errstate(divide="ignore"):
-        ulp_at = np.where(r != 0, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(np.where(finite, r, 1.0)), 1e-300))) - mant), 0.0)
+        mag = np.abs(np.where(finite, r, 1.0))
+        if bias is not None:
+            mag = np.maximum(mag, np.abs(np.where(finite, r - np.asarray(bias, dtype=np.float64)[None, :], 1.0)))
+        ulp_at = np.where(mag != 0, 2.0 ** (np.floor(np.log2(np.maximum(mag, 1e-300))) - mant), 0.0)
     excess = float(np.max(np.where(finite, np.abs(d) - ulp_at, 0.0))) if d.size else 0.0
     return {
         "max_excess_over_1ulp": max(excess, 0.0),

@@ -48,6 +48,33 @@ def gemm_ref_case(name):
 
 
 # ------------------------------------------------------------------------------------------------
+# GEMM cases with fp8e4m3fn weights (kernel/naive.py handles them through the same `b.to(float16)`; the reference's kernel
+# has an approximate e4m3 upcast, hip_kernel.cu:83-99).  Weights are drawn as byte codes, so no fp32 -> e4m3 cast is involved.
+# ------------------------------------------------------------------------------------------------
+GEMM_E4M3_CASES = {
+    # name: (M, N, K, out_dtype, seed)
+    "e4m3_48x256x256_bf16": (48, 256, 256, "bf16", 41),        # random finite codes
+    "e4m3_all_codes_fp16": (8, 256, 16, "fp16", 42),           # column n multiplies by code n alone: every value, subnormals and the two NaN codes
+}
+
+
+def gemm_e4m3_case(name):
+    M, N, K, out_dtype, seed = GEMM_E4M3_CASES[name]
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((M, K), dtype=np.float32).astype(np.float16)
+    if "all_codes" in name:
+        b_kn = np.zeros((K, N), dtype=np.uint8)
+        b_kn[0, :] = np.arange(256, dtype=np.uint8)
+        scale = np.float32(0.5)
+    else:
+        b_kn = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
+        b_kn = np.where((b_kn & 0x7F) == 0x7F, np.uint8(0x3A), b_kn).astype(np.uint8)      # no NaN codes here
+        scale = np.float32(2.0 ** -6)
+    bias = fo.from_f32(rng.standard_normal((N,), dtype=np.float32), out_dtype)
+    return {"a": a, "b_kn": b_kn, "b_prepacked": fo.prepack_b_for_scaled_mm(b_kn), "scale": scale, "bias": bias, "out_dtype": out_dtype}
+
+
+# ------------------------------------------------------------------------------------------------
 # GEMM cases on the benchmark distribution: A ~ N(0,1) fp16, W ~ N(0, 1/sqrt(K)) quantised through the loader path
 # (fp32 in, scale = amax/57344).  Verbatim naive.py overflows fp16 here; the fixture is the same op sequence with an
 # fp32 product, evaluated with torch in make_golden.py.

@@ -96,6 +96,24 @@ def main():
             assert rep["nonfinite_agree"]
             assert rep["fro_rel"] <= 0.01, (name, product, rep)
 
+    # ---- GEMM with fp8e4m3fn weights: verbatim scaled_mm_naive on a float8_e4m3fn tensor ------------------------------
+    codes = torch.arange(256, dtype=torch.uint8)
+    assert np.array_equal(np.nan_to_num(codes.view(torch.float8_e4m3fn).float().numpy(), nan=12345.0),
+                          np.nan_to_num(fo.e4m3_bits_to_f32(codes.numpy()), nan=12345.0)), "e4m3 decode restatement"
+    for name in cases.GEMM_E4M3_CASES:
+        c = cases.gemm_e4m3_case(name)
+        a = to_torch(c["a"], "fp16")
+        b_pp = torch.from_numpy(c["b_prepacked"]).view(torch.float8_e4m3fn)
+        scale = torch.tensor(float(c["scale"]), dtype=torch.float32)
+        bias = to_torch(c["bias"], c["out_dtype"])
+        ref_np = from_torch(naive.scaled_mm_naive(a, b_pp, scale, bias, TORCH_DT[c["out_dtype"]], b_prepacked=True))
+        out[f"gemm/{name}/out"] = ref_np
+        for product in ("fp16", "fp32"):
+            mine = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product=product, b_format="e4m3")
+            rep = fo.error_report(mine, ref_np, c["out_dtype"])
+            report.append((name, product, rep))
+            assert rep["nonfinite_agree"] and rep["fro_rel"] <= 0.01, (name, product, rep)
+
     # ---- GEMM, benchmark distribution: verbatim naive overflows; fixture = same ops with an fp32 product ---------
     for name in cases.GEMM_BENCH_CASES:
         c = cases.gemm_bench_case(name)

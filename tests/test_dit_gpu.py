@@ -44,7 +44,7 @@ def test_forward_against_cpu_forward_with_oracle_linears(pkg, native, cuda_dev, 
     for name, i, a16, y in seen:
         lin = cpu.blocks[i][name]
         ref = naive_torch.scaled_mm_cpu(a16, lin.q, lin.s, lin.b, torch.bfloat16)
-        assert_gemm_close(from_torch(y), from_torch(ref), "bf16", fo, f"block {i} {name}")
+        assert_gemm_close(from_torch(y), from_torch(ref), "bf16", fo, f"block {i} {name}", bias=lin.b.float().numpy())
     # (2) end to end
     y_cpu = cpu(x)
     got, ref = y_gpu.float().cpu(), y_cpu.float()

@@ -251,8 +251,12 @@ def test_argument_checks(hip_kernel, cuda_dev):
         op(a, b, None, torch.zeros(32, dtype=torch.bfloat16, device=cuda_dev), c, *cfg, 1)
     with pytest.raises(RuntimeError, match="c.shape\\[1\\] must equal N"):
         op(a, b, None, None, c[:, :16], *cfg, 1)
-    with pytest.raises(RuntimeError, match="fp8e4m3"):
-        op(a, b.view(torch.uint8).view(torch.float8_e4m3fn), None, None, c, *cfg, 0)
+    with pytest.raises(RuntimeError, match="float8_e5m2 when b_dtype=1"):
+        op(a, b.view(torch.uint8).view(torch.float8_e4m3fn), None, None, c, *cfg, 1)
+    with pytest.raises(RuntimeError, match="float8_e4m3fn when b_dtype=0"):
+        op(a, b, None, None, c, *cfg, 0)
+    with pytest.raises(RuntimeError, match="b_dtype must be 0"):
+        op(a, b, None, None, c, *cfg, 2)
     with pytest.raises(RuntimeError, match="a.stride\\(0\\) must equal K"):
         op(torch.zeros((64, 16), dtype=torch.float16, device=cuda_dev).t(), b, None, None, c, *cfg, 1)
 
@@ -267,7 +271,7 @@ def test_reference_c_abi_signature(native, cuda_dev):
     assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C) == 1
     torch.cuda.synchronize()
     assert_gemm_close(from_torch(C), fo.scaled_mm(a, bq, s, b, "fp16"), "fp16", fo)
-    assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C, b_dtype=0) == 0      # e4m3 is not supported
+    assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C, b_dtype=2) == 0      # neither e4m3 (0) nor e5m2 (1): refused like an unknown config
     # a handful of tokens through the same signature: the streaming kernel (this entry point has no workspace to split K through)
     C8 = torch.empty((8, 256), dtype=torch.float16, device=cuda_dev)
     assert native.launch_scaled_mm_reference_abi(A[:8].contiguous(), B, S, Bi, C8) == 1

@@ -111,3 +111,43 @@ def test_bf16_to_fp16(golden):
         mine = fo.from_f32(fo.bf16_bits_to_f32(pats), "fp16")
     nan_mask = np.isnan(mine)
     assert sha(np.where(nan_mask, np.uint16(0x7E00), mine.view(np.uint16))) == str(golden["convert/bf16_to_fp16_sha"])
+
+
+@pytest.mark.parametrize("name", list(cases.GEMM_E4M3_CASES))
+def test_gemm_e4m3_weights(golden, name):
+    """fp8e4m3fn weights: the oracle against verbatim kernel/naive.py run on a float8_e4m3fn tensor."""
+    c = cases.gemm_e4m3_case(name)
+    ref = golden[f"gemm/{name}/out"]
+    mine = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp16", b_format="e4m3")
+    rep = fo.error_report(mine, ref, c["out_dtype"])
+    assert rep["nonfinite_agree"] and rep["fro_rel"] <= 1e-5 and rep["mismatches"] <= max(ref.size // 1000, 2), rep
+    if "all_codes" in name:      # one product per output: nothing depends on a summation order
+        finite = ~np.isnan(fo.to_f32(ref, c["out_dtype"]))
+        assert np.array_equal(mine[finite], ref[finite]) and (~finite).sum() == 2 * ref.shape[0]
+
+
+def test_e4m3_decode_table():
+    import torch
+
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    got = fo.e4m3_bits_to_f32(codes)
+    assert np.array_equal(np.isnan(want), np.isnan(got)) and np.array_equal(got[~np.isnan(got)], want[~np.isnan(want)])
+    assert np.isnan(got[[0x7F, 0xFF]]).all() and got[0x7E] == 448.0 and got[0x01] == 2.0 ** -9
+
+
+def test_oracle_operand_and_result_types():
+    """bf16 activations multiplied as they are equal cast-first where the cast is exact; the final cast is one more rounding."""
+    rng = np.random.default_rng(0)
+    a32 = rng.standard_normal((8, 64), dtype=np.float32)
+    a_bf = fo.from_f32(a32, "bf16")
+    w = (rng.standard_normal((32, 64), dtype=np.float32) / 8).astype(np.float32)
+    bq, s = fo.make_feather_quantized_weight(w, "fp32", None)
+    direct = fo.scaled_mm(a_bf, bq, s, None, "bf16", a_format="bf16")
+    cast_first = fo.scaled_mm(a_bf, bq, s, None, "bf16", a_format="bf16_cast_first")
+    as_fp16 = fo.scaled_mm(fo.to_f32(a_bf, "bf16").astype(np.float16), bq, s, None, "bf16")
+    assert np.array_equal(cast_first, as_fp16)
+    assert fo.error_report(direct, cast_first, "bf16")["max_ulp"] <= 1           # randn may hold a few values below 2^-14
+    y16 = fo.scaled_mm(fo.to_f32(a_bf, "bf16").astype(np.float16), bq, s, None, "fp16")
+    y16_as_bf = fo.scaled_mm(fo.to_f32(a_bf, "bf16").astype(np.float16), bq, s, None, "fp16", final_dtype="bf16")
+    assert np.array_equal(y16_as_bf, fo.from_f32(fo.to_f32(y16, "fp16"), "bf16"))

@@ -30,7 +30,7 @@ def from_torch(t):
     return t.numpy().copy()
 
 
-def assert_gemm_close(got, ref, out_dtype, fo, what="", has_bias=True):
+def assert_gemm_close(got, ref, out_dtype, fo, what="", has_bias=True, bias=None):
     """The GEMM gate: |err| <= 1e-2 * rms(out) once the one-ulp rounding-boundary flips any two fp32-accumulating
     implementations show are set aside (they exceed 1e-2*rms by construction for bf16), Frobenius-relative error
     <= 1e-3, and inf/NaN in the same places.
@@ -39,8 +39,9 @@ def assert_gemm_close(got, ref, out_dtype, fo, what="", has_bias=True):
     elements whose bits differ from the oracle's stays below 1e-3 of the output for bf16 (the reference's own naive.py
     against the oracle shows 1e-4 at 256 x 1024 x 1024) and 8e-3 for fp16 (its ulp is 8 times finer against the same
     fp32 summation noise), and without a bias every differing element is exactly one ulp away (a bias add can cancel
-    and turn one ulp of the product into several of the sum).  The count is printed (pytest -s shows it)."""
-    rep = fo.error_report(got, ref, out_dtype)
+    and turn one ulp of the product into several of the sum).  `bias` (float32 values of the bias that was added, optional):
+    one ulp is then measured at the pre-bias magnitude where that is larger.  The count is printed (pytest -s shows it)."""
+    rep = fo.error_report(got, ref, out_dtype, bias=bias)
     size = int(np.asarray(got).size)
     limit = (1e-3 if out_dtype == "bf16" else 8e-3) * size + 4
     print(f"[gemm gate] {what}: {rep['mismatches']} of {size} elements differ from the oracle (limit {limit:.0f}), max {rep['max_ulp']} ulp, "
