@@ -262,9 +262,10 @@ def error_report(out, ref, out_dtype, bias=None):
     """max|err|, rms(ref), Frobenius-relative error and max ulp distance between two outputs of `out_dtype`.
 
     `bias` (the [N] bias that was added, as float32 values): the output is cvt(acc * scale) + bias with the rounding BEFORE
-    the bias add (naive.py:34-40), so a one-ulp rounding-boundary flip has the size of an ulp of the pre-bias value, which can
-    be twice the ulp of the final value when the add crosses a binade downwards.  With `bias` given, "one ulp" is taken at
-    the larger of the two magnitudes."""
+    the bias add (naive.py:34-40) and a second rounding after it.  A one-ulp rounding-boundary flip of the first rounding has
+    the size of an ulp of the pre-bias value (which can be twice the ulp of the final value when the add crosses a binade
+    downwards), and the second rounding can send the two candidates to neighbours that are one more ulp apart.  With `bias`
+    given, the allowance is therefore two ulps, taken at the larger of the pre- and post-bias magnitudes."""
     o = to_f32(out, out_dtype).astype(np.float64)
     r = to_f32(ref, out_dtype).astype(np.float64)
     finite = np.isfinite(r) & np.isfinite(o)
@@ -284,7 +285,7 @@ def error_report(out, ref, out_dtype, bias=None):
         mag = np.abs(np.where(finite, r, 1.0))
         if bias is not None:
             mag = np.maximum(mag, np.abs(np.where(finite, r - np.asarray(bias, dtype=np.float64)[None, :], 1.0)))
-        ulp_at = np.where(mag != 0, 2.0 ** (np.floor(np.log2(np.maximum(mag, 1e-300))) - mant), 0.0)
+        ulp_at = np.where(mag != 0, 2.0 ** (np.floor(np.log2(np.maximum(mag, 1e-300))) - mant), 0.0) * (2.0 if bias is not None else 1.0)
     excess = float(np.max(np.where(finite, np.abs(d) - ulp_at, 0.0))) if d.size else 0.0
     return {
         "max_excess_over_1ulp": max(excess, 0.0),

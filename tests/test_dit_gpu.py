@@ -112,16 +112,27 @@ def test_row_parallel_pieces_on_one_gpu(native, cuda_dev, M, N, K, g):
         native.scaled_mm_scatter_into(A[:, r * kl:(r + 1) * kl].contiguous(), B[r * kl // 16:(r + 1) * kl // 16].contiguous(), S,
                                       [partials[d][r] for d in range(g)], rows)
     outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_dev) for _ in range(g)]
+    plain = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
     for d in range(g):
         native.reduce_partials_into(partials[d], Bi, res[d * rows:(d + 1) * rows], [o[d * rows:(d + 1) * rows] for o in outs])
+        native.reduce_partials_into(partials[d], None, None, [plain[d * rows:(d + 1) * rows]])
     native.check_device_status(cuda_dev)
     for o in outs[1:]:
         assert torch.equal(o.view(torch.int16), outs[0].view(torch.int16))
-    # every partial must be the oracle's partial GEMM bit-compatible under the gate (no bias), and the sum the full result
-    ref_full = fo.scaled_mm(a, bq, s, bias, "bf16", product="fp32")
-    ref = (to_torch(ref_full, "bf16").float() + res.cpu().float()).to(torch.bfloat16)
-    rep = fo.error_report(from_torch(outs[0]), from_torch(ref), "bf16")
-    print(f"[row-parallel] {(M, N, K, g)}: {rep}")
-    assert rep["nonfinite_agree"] and rep["fro_rel"] <= 2e-3 and rep["max_excess_over_1ulp"] <= 1e-2 * rep["rms"], rep
+    # the reduce kernel, bit for bit: fp32 sum of the g partials in rank order, one rounding, + bias, + residual in bf16
+    stacked = torch.cat(partials, dim=1)                                       # [g sources, M, N]: owner d's rows are rows d*rows..
+    acc = torch.zeros((M, N), dtype=torch.float32, device=cuda_dev)
+    for src in range(g):
+        acc += stacked[src].float()
+    emulated = acc.to(torch.bfloat16)
+    assert torch.equal(plain.view(torch.int16), emulated.view(torch.int16))
+    emulated = (emulated + Bi) + res
+    assert torch.equal(outs[0].view(torch.int16), emulated.view(torch.int16))
+    # every partial is an ordinary GEMM over a K slice, and their sum is the full result within the gate: K is split, so the
+    # g roundings of the partials (each a fraction 1/sqrt(g) of the output's size) come on top of the final one
     p0 = fo.scaled_mm(a[:, :kl], bq[: kl // 16], s, None, "bf16", product="fp32")
-    assert_gemm_close(from_torch(torch.cat([partials[d][0] for d in range(g)])), p0, "bf16", fo, "partial of rank 0", has_bias=False)
+    assert_gemm_close(from_torch(stacked[0]), p0, "bf16", fo, "partial of rank 0")
+    ref_full = fo.scaled_mm(a, bq, s, None, "bf16", product="fp32")
+    rep = fo.error_report(from_torch(plain), ref_full, "bf16")
+    print(f"[row-parallel] {(M, N, K, g)}: {rep}")
+    assert rep["nonfinite_agree"] and rep["fro_rel"] <= 3e-3 and rep["max_excess_over_1ulp"] <= 1e-2 * rep["rms"], rep

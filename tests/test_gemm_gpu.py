@@ -55,7 +55,7 @@ def test_reference_distribution_through_operator(golden, hip_kernel, native, cud
         rep = fo.error_report(got, golden[f"gemm/{name}/out"], c["out_dtype"])
         assert rep["fro_rel"] <= 0.01 and rep["max_abs"] <= (2.0 if c["out_dtype"] == "fp16" else 16.0), rep
         ref32 = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp32")
-        assert_gemm_close(got, ref32, c["out_dtype"], fo, name)
+        assert_gemm_close(got, ref32, c["out_dtype"], fo, name, bias=c["bias"])
 
 
 @pytest.mark.parametrize("name", list(cases.GEMM_BENCH_CASES))
@@ -71,9 +71,9 @@ def test_benchmark_distribution(golden, hip_kernel, native, cuda_dev, name):
     native.check_device_status(cuda_dev)
     got = from_torch(out)
     rows = golden[f"gemm/{name}/rows"]
-    assert_gemm_close(got[rows], golden[f"gemm/{name}/out_rows"], c["out_dtype"], fo, name + " vs fixture", has_bias=c["bias"] is not None)
+    assert_gemm_close(got[rows], golden[f"gemm/{name}/out_rows"], c["out_dtype"], fo, name + " vs fixture", bias=c["bias"])
     ref = fo.scaled_mm(c["a"], c["b_prepacked"], c["scale"], c["bias"], c["out_dtype"], product="fp32")
-    assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle", has_bias=c["bias"] is not None)
+    assert_gemm_close(got, ref, c["out_dtype"], fo, name + " vs oracle", bias=c["bias"])
 
 
 # (M, N, K, out_dtype, (tokens_tile, cta_pair, split_k, transform_groups, max_ctas[, kernel, staging]), bias, scale)
@@ -114,7 +114,7 @@ def test_variants_against_oracle(native, cuda_dev, M, N, K, out_dtype, variant, 
     a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 7 + N * 3 + K, bias=bias)
     got = _run(native, cuda_dev, a, bq, s if scale else None, b, out_dtype, variant)
     ref = fo.scaled_mm(a, bq, s if scale else None, b, out_dtype, product="fp32")
-    assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}", has_bias=bias)
+    assert_gemm_close(got, ref, out_dtype, fo, f"{(M, N, K, variant)}", bias=b)
 
 
 STREAM_CASES = [
@@ -139,16 +139,16 @@ def test_streaming_kernel_against_oracle(native, cuda_dev, M, N, K, out_dtype, b
     a, bq, s, b = _synthetic(M, N, K, out_dtype, seed=M * 11 + N + K, bias=bias)
     ref = fo.scaled_mm(a, bq, s, b, out_dtype, product="fp32")
     forced = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_STREAM))
-    assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}", has_bias=bias)
+    assert_gemm_close(forced, ref, out_dtype, fo, f"forced {(M, N, K)}", bias=b)
     auto = _run(native, cuda_dev, a, bq, s, b, out_dtype, None)
     if M <= 16:     # the library's own choice up to 16 tokens; above, the tensor-memory kernel measured faster
         assert np.array_equal(auto, forced)
         assert native.choose_variant(M, N, K).kernel == native.KERNEL_STREAM
     else:
-        assert_gemm_close(auto, ref, out_dtype, fo, f"auto {(M, N, K)}", has_bias=bias)
+        assert_gemm_close(auto, ref, out_dtype, fo, f"auto {(M, N, K)}", bias=b)
         assert native.choose_variant(M, N, K).kernel == native.KERNEL_TMEM
     tmem = _run(native, cuda_dev, a, bq, s, b, out_dtype, (0, 0, 0, 0, 0, native.KERNEL_TMEM))
-    assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}", has_bias=bias)
+    assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}", bias=b)
 
 
 def test_streaming_kernel_rejects_many_tokens(native, cuda_dev):
@@ -163,7 +163,7 @@ def test_split_k_workspace_is_reusable(native, cuda_dev):
     ref = fo.scaled_mm(a, bq, s, b, "bf16", product="fp32")
     for _ in range(3):
         got = _run(native, cuda_dev, a, bq, s, b, "bf16", (64, 1, 4, 2, 0))
-        assert_gemm_close(got, ref, "bf16", fo)
+        assert_gemm_close(got, ref, "bf16", fo, bias=b)
     # the tile counters occupy the first 64 KiB of the workspace
     ws = native.workspace_for(cuda_dev)
     assert int(ws[:65536].view(torch.int32).abs().sum().item()) == 0
@@ -173,10 +173,10 @@ def test_split_k_launches_of_different_tile_counts_share_a_workspace(native, cud
     """A launch with few tiles followed by one with many: the second one's counters must not see the first one's partials."""
     a, bq, s, b = _synthetic(16, 256, 2048, "bf16", seed=31)
     got = _run(native, cuda_dev, a, bq, s, b, "bf16", (16, 1, 4, 2, 0))
-    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo, bias=b)
     a, bq, s, b = _synthetic(16, 13824, 1024, "bf16", seed=32)
     got = _run(native, cuda_dev, a, bq, s, b, "bf16", (16, 1, 4, 2, 0))
-    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo, bias=b)
 
 
 def test_split_k_on_two_streams_does_not_share_a_workspace(native, cuda_dev):
@@ -202,7 +202,7 @@ def test_split_k_on_two_streams_does_not_share_a_workspace(native, cuda_dev):
     ws = {native.workspace_for(cuda_dev, st.cuda_stream).data_ptr() for st, *_ in work}
     assert len(ws) == 2
     for st, A, B, S, Bi, C, v, ref in work:
-        assert_gemm_close(from_torch(C), ref, "bf16", fo, f"stream {st.cuda_stream:#x}")
+        assert_gemm_close(from_torch(C), ref, "bf16", fo, f"stream {st.cuda_stream:#x}", has_bias=True)
 
 
 def test_tile_variants_agree_bitwise(native, cuda_dev):
@@ -215,7 +215,7 @@ def test_tile_variants_agree_bitwise(native, cuda_dev):
     for outs in (one_issuer, two_issuers):
         for o in outs[1:]:
             assert np.array_equal(o, outs[0])
-    assert_gemm_close(two_issuers[0], fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo)
+    assert_gemm_close(two_issuers[0], fo.scaled_mm(a, bq, s, b, "bf16"), "bf16", fo, bias=b)
 
 
 def test_empty_and_edge_shapes(hip_kernel, native, cuda_dev):
@@ -270,7 +270,7 @@ def test_reference_c_abi_signature(native, cuda_dev):
     C = torch.empty((64, 256), dtype=torch.float16, device=cuda_dev)
     assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C) == 1
     torch.cuda.synchronize()
-    assert_gemm_close(from_torch(C), fo.scaled_mm(a, bq, s, b, "fp16"), "fp16", fo)
+    assert_gemm_close(from_torch(C), fo.scaled_mm(a, bq, s, b, "fp16"), "fp16", fo, bias=b)
     assert native.launch_scaled_mm_reference_abi(A, B, S, Bi, C, b_dtype=2) == 0      # neither e4m3 (0) nor e5m2 (1): refused like an unknown config
     # a handful of tokens through the same signature: the streaming kernel (this entry point has no workspace to split K through)
     C8 = torch.empty((8, 256), dtype=torch.float16, device=cuda_dev)
@@ -279,7 +279,7 @@ def test_reference_c_abi_signature(native, cuda_dev):
     stream8 = torch.empty_like(C8)
     native.scaled_mm_into(A[:8].contiguous(), B, S, Bi, stream8, variant=native.make_variant(kernel=native.KERNEL_STREAM))
     assert torch.equal(C8, stream8)
-    assert_gemm_close(from_torch(C8), fo.scaled_mm(a[:8], bq, s, b, "fp16"), "fp16", fo)
+    assert_gemm_close(from_torch(C8), fo.scaled_mm(a[:8], bq, s, b, "fp16"), "fp16", fo, bias=b)
 
 
 def test_column_shard_writes_in_place(native, cuda_dev):
@@ -355,7 +355,7 @@ def test_full_size_wan_shapes_properties(native, cuda_dev, K, N):
     native.check_device_status(cuda_dev)
     rows = np.unique(np.concatenate([np.arange(0, M, 4099), [M - 1, 255, 256, M - 257]]))
     ref = fo.scaled_mm(from_torch(A[rows]), from_torch(B), np.float32(S.item()), None, "bf16", product="fp32")
-    assert_gemm_close(from_torch(C[rows]), ref, "bf16", fo, "sampled rows", has_bias=False)
+    assert_gemm_close(from_torch(C[rows]), ref, "bf16", fo, "sampled rows")
     # linearity in powers of two is exact (no overflow at this scale)
     C2 = torch.empty_like(C)
     native.scaled_mm_into(A * 2, B, S, None, C2)
@@ -373,7 +373,7 @@ def test_small_m_sweep(native, cuda_dev, M, K, N):
     """The bandwidth-bound sweep of the benchmark, full K and N, checked in full against the oracle."""
     a, bq, s, _ = _synthetic(M, N, K, "bf16", seed=M + K, bias=False)
     got = _run(native, cuda_dev, a, bq, s, None, "bf16")
-    assert_gemm_close(got, fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"M={M}", has_bias=False)
+    assert_gemm_close(got, fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"M={M}")
 
 
 @pytest.mark.parametrize("K,N", [(3072, 3072), (3072, 9216), (3072, 12288), (12288, 3072)])
@@ -383,7 +383,7 @@ def test_qwen_image_shapes(native, cuda_dev, K, N):
     a, bq, s, _ = _synthetic(M, N, K, "fp16", seed=K + N, bias=False)
     got = _run(native, cuda_dev, a, bq, s, None, "fp16")
     rows = np.arange(0, M, 68)
-    assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}", has_bias=False)
+    assert_gemm_close(got[rows], fo.scaled_mm(a[rows], bq, s, None, "fp16"), "fp16", fo, f"{K}x{N}")
 
 
 @pytest.mark.parametrize("args", [["300", "520", "1040", "--bias", "--check", "--iters", "5"], ["16", "1024", "2048", "--fp16", "--check", "--iters", "5"],

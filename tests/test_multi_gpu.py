@@ -83,7 +83,9 @@ def _worker(rank, world, port, tmpdir):
         out = row(a2[:, rank * kl:(rank + 1) * kl].contiguous(), torch.bfloat16, residual=res)
         torch.cuda.synchronize()
         rep = fo.error_report(from_torch(out), from_torch(full2), "bf16")
-        check(f"row-parallel call {call} {rep}", rep["nonfinite_agree"] and rep["fro_rel"] <= 2e-3 and rep["max_excess_over_1ulp"] <= 1e-2 * rep["rms"])
+        # bias and residual are each added with a rounding of their own after the partials were summed: up to an ulp more per
+        # step on top of the K-split noise that tests/test_dit_gpu.py bounds by 1e-2 * rms without them
+        check(f"row-parallel call {call} {rep}", rep["nonfinite_agree"] and rep["fro_rel"] <= 4e-3 and rep["max_excess_over_1ulp"] <= 4e-2 * rep["rms"])
         check(f"row-parallel call {call} identical on all ranks", same_on_all_ranks(out))
 
     # the DiT harness: all-gather mode is bitwise the one-rank forward, pairs mode is within tolerance and identical on all ranks

@@ -50,7 +50,7 @@ def test_load_and_forward(ops_mod, cuda_dev, src_dtype, out_dtype):
     assert np.array_equal(from_torch(lin.weight._qdata), q_ref)
     ref = fo.scaled_mm(x.reshape(-1, K), q_ref, s_ref, fo.from_f32(bias, out_dtype), out_dtype)
     ref16 = fo.from_f32(fo.to_f32(ref, out_dtype), "fp16")        # y.to(dtype_orig)
-    assert_gemm_close(from_torch(y.reshape(-1, N)), ref16, "fp16", fo)
+    assert_gemm_close(from_torch(y.reshape(-1, N)), ref16, "fp16", fo, bias=bias)
 
 
 def test_e5m2_checkpoint_with_scale_keys(ops_mod, cuda_dev):

@@ -69,7 +69,7 @@ def test_bf16_activations_equal_cast_first_where_the_cast_is_exact(native, cuda_
     ref_np = fo.scaled_mm(from_torch(x), bq, s, None, "bf16", a_format="bf16")
     got = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_dev)
     native.scaled_mm_typed_into(x, B, S, None, got)
-    assert_gemm_close(from_torch(got), ref_np, "bf16", fo, f"bf16 activations {(M, N, K)}", has_bias=False)
+    assert_gemm_close(from_torch(got), ref_np, "bf16", fo, f"bf16 activations {(M, N, K)}")
 
 
 def test_bf16_activations_outside_the_fp16_range(native, cuda_dev):
@@ -88,7 +88,7 @@ def test_bf16_activations_outside_the_fp16_range(native, cuda_dev):
     got = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_dev)
     native.scaled_mm_typed_into(x, B, S, None, got)
     native.check_device_status(cuda_dev)
-    assert_gemm_close(from_torch(got), fo.scaled_mm(from_torch(x), bq, s, None, "bf16", a_format="bf16"), "bf16", fo, "unrounded bf16", has_bias=False)
+    assert_gemm_close(from_torch(got), fo.scaled_mm(from_torch(x), bq, s, None, "bf16", a_format="bf16"), "bf16", fo, "unrounded bf16")
     cast_first = fo.to_f32(fo.scaled_mm(from_torch(x), bq, s, None, "bf16", a_format="bf16_cast_first"), "bf16")
     assert not np.isfinite(cast_first[3]).all() and torch.isfinite(got[3].float()).all()
 
@@ -136,6 +136,6 @@ def test_operator_linear_folds_both_casts(pkg, native, hip_kernel, cuda_dev):
         y = lin(x)
         native.check_device_status(cuda_dev)
         assert y.dtype == torch.bfloat16 and y.shape == (2, T, N)
-        ref = hip_kernel.scaled_mm_hip(x.reshape(-1, K).to(torch.float16), lin.weight._qdata, lin.weight._params.scale.to(cuda_dev).reshape(1).float(),
-                                       lin.bias, torch.float16).to(torch.bfloat16)
+        ref = hip_kernel.scaled_mm_hip(x.reshape(-1, K).to(torch.float16), lin.weight._qdata.to(cuda_dev), lin.weight._params.scale.to(cuda_dev).reshape(1).float(),
+                                       lin.bias.to(cuda_dev), torch.float16).to(torch.bfloat16)
         assert torch.equal(y.reshape(-1, N).view(torch.int16), ref.view(torch.int16)), T

@@ -42,7 +42,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice(native, cuda_dev):
         native.scaled_mm_static_into(A, B, S, Bi, got, variant=variant)
         native.check_device_status(cuda_dev)
         assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), f"call {call}"
-        assert_gemm_close(from_torch(got), fo.scaled_mm(a, bq, s, bias, "bf16"), "bf16", fo, f"call {call}")
+        assert_gemm_close(from_torch(got), fo.scaled_mm(a, bq, s, bias, "bf16"), "bf16", fo, f"call {call}", bias=bias)
 
 
 def test_static_scratch_entry_with_library_chosen_variant(native, cuda_dev):
@@ -64,7 +64,7 @@ def test_static_scratch_entry_with_library_chosen_variant(native, cuda_dev):
             native.scaled_mm_into(A, B, S, None, ref, variant=None if M <= 16 else same_choice)
             native.check_device_status(cuda_dev)
             assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), (M, N, K)
-        assert_gemm_close(from_torch(got), fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"{(M, N, K)}", has_bias=False)
+        assert_gemm_close(from_torch(got), fo.scaled_mm(a, bq, s, None, "bf16"), "bf16", fo, f"{(M, N, K)}")
 
 
 def test_static_scratch_entry_rejects_oversized_requests(native, cuda_dev):

@@ -30,28 +30,36 @@ def from_torch(t):
     return t.numpy().copy()
 
 
-def assert_gemm_close(got, ref, out_dtype, fo, what="", has_bias=True, bias=None):
-    """The GEMM gate: |err| <= 1e-2 * rms(out) once the one-ulp rounding-boundary flips any two fp32-accumulating
-    implementations show are set aside (they exceed 1e-2*rms by construction for bf16), Frobenius-relative error
-    <= 1e-3, and inf/NaN in the same places.
+def assert_gemm_close(got, ref, out_dtype, fo, what="", bias=None, has_bias=None):
+    """The GEMM gate.  `bias`: the bias that was added, as the storage array of `out_dtype` (or float32 values), or None.
 
-    The flips themselves are bounded too, so a wrong rounding mode cannot hide under the Frobenius bound: the number of
-    elements whose bits differ from the oracle's stays below 1e-3 of the output for bf16 (the reference's own naive.py
-    against the oracle shows 1e-4 at 256 x 1024 x 1024) and 8e-3 for fp16 (its ulp is 8 times finer against the same
-    fp32 summation noise), and without a bias every differing element is exactly one ulp away (a bias add can cancel
-    and turn one ulp of the product into several of the sum).  `bias` (float32 values of the bias that was added, optional):
-    one ulp is then measured at the pre-bias magnitude where that is larger.  The count is printed (pytest -s shows it)."""
+    1. |err| <= 1e-2 * rms(out) once rounding-boundary flips are set aside: two correct fp32-accumulating evaluations round a
+       value that sits on a boundary of the output dtype to different neighbours, and one bf16 ulp at |out| >= 2 rms already
+       exceeds 1e-2 * rms, so the literal bound cannot hold for bf16 by any implementation.  Without a bias the allowance is
+       one ulp of the oracle's value; with a bias two ulps at the larger of the pre- and post-bias magnitudes (the flip
+       happens before the add and the second rounding can widen it; see error_report).
+    2. Without a bias, what is left after the one-ulp allowance must be fp32 summation noise: <= 1e-4 * rms.  (A count of
+       ulps cannot be bounded: where a sum cancels to nearly zero its ulp shrinks below the noise of the fp32 additions.)
+    3. The number of elements whose bits differ from the oracle's (which rounds the exact sum once) is bounded: the chance
+       of a flip is about (fp32 summation noise) / (output ulp), i.e. some 1e-3 for bf16 at K = 5120 and 3e-2 for fp16 at
+       K = 12288 (measured), so at most 1 % of the elements for bf16 and 8 % for fp16.  A wrong rounding mode (truncation,
+       say) flips about half of all elements and fails this by a wide margin.  The count is printed (pytest -s shows it).
+    4. Frobenius-relative error <= 1e-3; inf/NaN in the same places; for fp16 also the literal max|err| <= 1e-2 * rms.
+    """
+    if bias is not None and np.asarray(bias).dtype != np.float32:
+        bias = fo.to_f32(bias, out_dtype)
+    if has_bias is None:
+        has_bias = bias is not None
     rep = fo.error_report(got, ref, out_dtype, bias=bias)
     size = int(np.asarray(got).size)
-    limit = (1e-3 if out_dtype == "bf16" else 8e-3) * size + 4
+    limit = (1e-2 if out_dtype == "bf16" else 8e-2) * size + 4
     print(f"[gemm gate] {what}: {rep['mismatches']} of {size} elements differ from the oracle (limit {limit:.0f}), max {rep['max_ulp']} ulp, "
-          f"fro_rel {rep['fro_rel']:.2e}")
+          f"beyond the ulp allowance {rep['max_excess_over_1ulp']:.2e}, fro_rel {rep['fro_rel']:.2e}, rms {rep['rms']:.3g}")
+    rms = max(rep["rms"], 1e-30)
     assert rep["nonfinite_agree"], (what, rep)
-    assert rep["max_excess_over_1ulp"] <= 1e-2 * max(rep["rms"], 1e-30), (what, rep)
+    assert rep["max_excess_over_1ulp"] <= (1e-2 if has_bias else 1e-4) * rms, (what, rep)
     assert rep["fro_rel"] <= 1e-3, (what, rep)
     assert rep["mismatches"] <= limit, (what, rep)
-    if not has_bias:
-        assert rep["max_ulp"] <= 1, (what, rep)
     if out_dtype == "fp16":
-        assert rep["max_abs"] <= 1e-2 * max(rep["rms"], 1e-30), (what, rep)
+        assert rep["max_abs"] <= 1e-2 * rms, (what, rep)
     return rep
