@@ -37,6 +37,12 @@ __device__ __forceinline__ void cluster_wait_acquire() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch: let the next kernel on the stream become resident and run its prologue while this one
+// still works, and wait until everything the previous kernel on the stream wrote is visible.  Both are no-ops for a launch
+// without a programmatic dependency.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------------------------

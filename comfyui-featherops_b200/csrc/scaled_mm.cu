@@ -333,6 +333,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_wring = tmem_base + C::kAccCols;   // column offset of the upcast-weight ring
+    // Everything above (barriers, tensor memory, tensor-map prefetch) touched no global memory and may have run while the
+    // previous kernel on the stream was still draining (programmatic dependent launch); from here on its results are needed.
+    pdl_launch_dependents();
+    pdl_wait_for_previous_kernel();
 
     if (warp == kProducerWarp || warp == kWProducerWarp) {
         // ------------------------------------------------------------------ TMA producers (one lane each): token tiles / weight bytes
@@ -1172,13 +1176,16 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     cfg.blockDim = dim3(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CG;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // the CTAs may become resident and set up while the previous kernel on the stream drains; see pdl_wait_for_previous_kernel
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, p);
 }
 
@@ -1194,7 +1201,8 @@ static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMa
 }
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                   int output_dtype, int flip_final, int sms, cudaStream_t stream);   // small_m.cu
+                   int output_dtype, int flip_final, int sms, void* workspace, size_t workspace_bytes, cudaStream_t stream);   // small_m.cu
+size_t small_m_workspace_bytes(int64_t M, int64_t N, int64_t K, int sms);                                                    // small_m.cu
 
 // Operand and result types beyond the reference's fp16 x e5m2 -> out dtype.
 struct Types {
@@ -1247,7 +1255,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     // the streaming kernel multiplies fp16 activations by e5m2 weights only; the other operand types take the tensor-memory kernel
     const bool plain_operands = !types.a_bf16 && !types.w_e4m3;
     if (plain_operands && takes_streaming_kernel(variant, M, n_extra))
-        return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, flip_final, sms, stream);
+        return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, flip_final, sms, workspace, workspace_bytes, stream);
     if (which == FEATHER_KERNEL_STREAM)
         return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer and takes fp16 activations and e5m2 weights");
     Plan pl;
@@ -1477,10 +1485,15 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (M < 0 || N <= 0 || K <= 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "M, N, K must be positive");
     if (M == 0) return FEATHER_OK;
-    // The register-streaming kernel needs no scratch at all: when the library (or the caller) picks it, nothing of the
-    // built-in array is touched and the call is exactly feather_scaled_mm_ex's.
-    if (takes_streaming_kernel(variant, M, 0))
-        return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, nullptr, 0, status_dev, stream);
+    // The register-streaming kernel splits K across CTAs through the scratch when the weight's columns alone cannot fill the
+    // SMs; it gets the built-in array like the tensor-memory kernel below, with the counter block cleared first.
+    if (takes_streaming_kernel(variant, M, 0)) {
+        void* scratch = nullptr;
+        if (int st = static_scratch_of_current_device(&scratch)) return st;
+        const cudaError_t e = cudaMemsetAsync(scratch, 0, kCounterBytes, stream);
+        if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "clearing the tile counters failed: %s", cudaGetErrorString(e));
+        return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, scratch, kStaticScratchBytes, status_dev, stream);
+    }
     const int sms = sm_count_of_current_device();
     if (sms <= 0) return set_error(FEATHER_ERR_NO_DEVICE, "no CUDA device");
     // The same plan feather_scaled_mm_ex makes when it is handed a workspace of this size: a K split the library chose
@@ -1508,6 +1521,7 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
 extern "C" size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     int sms = sm_count_of_current_device();
+    if (takes_streaming_kernel(variant, M, 0)) return small_m_workspace_bytes(M, N, K, sms);
     Plan pl;
     if (!make_plan(M, N, K, variant, 0, false, sms, &pl)) return 0;
     return pl.ws_bytes;

@@ -12,6 +12,12 @@
 //   reduce      the 16 warps' fp32 partials go through shared memory and are added in warp order (deterministic), then
 //               * scale -> RTNE -> + bias in the output dtype, as in the tensor-memory kernel
 //
+//   K split     when the strips alone cannot fill the SMs in full rounds (N = 5120: 320 strips of 16 columns on 148 SMs), ks CTAs
+//               share a work item, each over 1/ks of K; a CTA parks its fp32 partial in the caller's workspace and the last
+//               of the ks to arrive (a counter per item) adds the partials in slice order - deterministic - and finishes
+//   launch      with programmatic dependent launch: the CTAs may become resident and run their prologue while the previous
+//               kernel on the stream drains; nothing touches global memory before griddepcontrol.wait
+//
 // Same math as kernel/hip/hip_kernel.cu:125-420 of the reference (which has no small-M path: its README.md:31 names an
 // unshipped split-k branch).
 #include <cuda_bf16.h>
@@ -23,11 +29,44 @@
 
 #include "../../include/feather_b200.h"
 #include "host_util.h"
+#include "ptx.cuh"
 
 namespace feather {
 
 constexpr int kSmWarps = 16;
 constexpr int kSmThreads = kSmWarps * 32;
+constexpr size_t kSmCounterBytes = 65536;     // tile counters at the start of the workspace (same layout as the tensor-memory kernel's)
+
+
+struct SplitArgs {
+    int ks;              // CTAs per work item (K slices); 1 = no split, the pointers are unused
+    float* partials;     // [item][slice][tokens][columns] fp32
+    int* counters;       // [item], zero on entry, left at zero
+};
+
+// Cross-CTA part of a K split, run by all threads of the CTA after its own 16 warps' partials are in shared memory (`red`,
+// summed in warp order by `sum_of`).  Returns through `emit(tok, col, value)` for the elements this thread finishes, which
+// happens in the last CTA of the item to arrive; the others only park their partial.
+template <int kTok, int kCols, typename SumFn, typename EmitFn>
+__device__ __forceinline__ void split_finish(const SplitArgs& sp, int group, int slice, int* flag_smem, SumFn sum_of, EmitFn emit) {
+    float* const mine = sp.partials + (static_cast<long long>(group) * sp.ks + slice) * (kTok * kCols);
+    for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) __stcg(mine + o, sum_of(o / kCols, o % kCols));
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *flag_smem = (atomicAdd(sp.counters + group, 1) == sp.ks - 1) ? 1 : 0;
+    __syncthreads();
+    if (*flag_smem != 0) {
+        __threadfence();
+        const float* const all = sp.partials + static_cast<long long>(group) * sp.ks * (kTok * kCols);
+        for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) {
+            float sum = 0.0f;
+            for (int sl = 0; sl < sp.ks; ++sl) sum += __ldcg(all + sl * (kTok * kCols) + o);     // slice order: deterministic
+            emit(o / kCols, o % kCols, sum);
+        }
+        if (threadIdx.x == 0) sp.counters[group] = 0;     // ready for the next launch
+    }
+    __syncthreads();
+}
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -59,22 +98,30 @@ __device__ __forceinline__ uint16_t sm_finish(float acc, float scale, int out_mo
 template <int MT, int P, int U>
 __global__ void __launch_bounds__(kSmThreads, 1)
 small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, const float* __restrict__ scale_ptr,
-               const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items) {
+               const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items,
+               SplitArgs sp) {
     constexpr int kTok = MT * 16;
     constexpr int kCols = P * 8;
     constexpr int kPitch = kCols + 1;
     extern __shared__ float red[];                          // [kSmWarps][kTok][kPitch]
+    __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int nkb = K / 16;
-    const int kb_begin = static_cast<int>(static_cast<long long>(warp) * nkb / kSmWarps);
-    const int kb_end = static_cast<int>(static_cast<long long>(warp + 1) * nkb / kSmWarps);
+    pdl_launch_dependents();
+    pdl_wait_for_previous_kernel();
     const float scale = scale_ptr != nullptr ? __ldg(scale_ptr) : 1.0f;
     const bool has_bias = bias != nullptr;
 
     for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-        const int n_base = item * kCols;
+        // item = (group of P strips, K slice); the slice's k16-blocks are split over the 16 warps
+        const int group = item / sp.ks, slice = item - group * sp.ks;
+        const int sl_begin = static_cast<int>(static_cast<long long>(slice) * nkb / sp.ks);
+        const int sl_end = static_cast<int>(static_cast<long long>(slice + 1) * nkb / sp.ks);
+        const int kb_begin = sl_begin + static_cast<int>(static_cast<long long>(warp) * (sl_end - sl_begin) / kSmWarps);
+        const int kb_end = sl_begin + static_cast<int>(static_cast<long long>(warp + 1) * (sl_end - sl_begin) / kSmWarps);
+        const int n_base = group * kCols;
         float acc[MT][P][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -148,18 +195,25 @@ small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, co
                 mine[(mt * 16 + g + 8) * kPitch + s * 8 + 2 * j + 1] = acc[mt][s][3];
             }
         __syncthreads();
-        for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) {
-            const int tok = o / kCols, col = o % kCols;
+        auto sum_of = [&](int tok, int col) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (kTok * kPitch) + tok * kPitch + col];   // warp order: deterministic
+            return sum;
+        };
+        auto emit = [&](int tok, int col, float sum) {
             const int n = n_base + col;
             if (tok < M && n < N) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (kTok * kPitch) + tok * kPitch + col];   // warp order: deterministic
                 const uint16_t bias_bits = has_bias ? __ldg(bias + n) : uint16_t(0);
                 c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16, has_bias, bias_bits);
             }
+        };
+        if (sp.ks == 1) {
+            for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) emit(o / kCols, o % kCols, sum_of(o / kCols, o % kCols));
+            __syncthreads();
+        } else {
+            split_finish<kTok, kCols>(sp, group, slice, &last_flag, sum_of, emit);
         }
-        __syncthreads();
     }
 }
 
@@ -168,21 +222,28 @@ small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, co
 template <int P, int U>
 __global__ void __launch_bounds__(kSmThreads, 1)
 small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, const float* __restrict__ scale_ptr,
-                const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items) {
+                const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items,
+                SplitArgs sp) {
     constexpr int kCols = P * 16;
     constexpr int kPitch = kCols + 1;
     extern __shared__ float red[];                          // [kSmWarps][8 tokens][kPitch]
+    __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int nkb = K / 16;
-    const int kb_begin = static_cast<int>(static_cast<long long>(warp) * nkb / kSmWarps);
-    const int kb_end = static_cast<int>(static_cast<long long>(warp + 1) * nkb / kSmWarps);
+    pdl_launch_dependents();
+    pdl_wait_for_previous_kernel();
     const float scale = scale_ptr != nullptr ? __ldg(scale_ptr) : 1.0f;
     const bool has_bias = bias != nullptr;
 
     for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-        const int n_base = item * kCols;
+        const int group = item / sp.ks, slice = item - group * sp.ks;
+        const int sl_begin = static_cast<int>(static_cast<long long>(slice) * nkb / sp.ks);
+        const int sl_end = static_cast<int>(static_cast<long long>(slice + 1) * nkb / sp.ks);
+        const int kb_begin = sl_begin + static_cast<int>(static_cast<long long>(warp) * (sl_end - sl_begin) / kSmWarps);
+        const int kb_end = sl_begin + static_cast<int>(static_cast<long long>(warp + 1) * (sl_end - sl_begin) / kSmWarps);
+        const int n_base = group * kCols;
         float acc[P][4];
 #pragma unroll
         for (int s = 0; s < P; ++s)
@@ -241,105 +302,155 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
             mine[(2 * j + 1) * kPitch + s * 16 + g + 8] = acc[s][3];
         }
         __syncthreads();
-        for (int o = threadIdx.x; o < 8 * kCols; o += kSmThreads) {
-            const int tok = o / kCols, col = o % kCols;
+        auto sum_of = [&](int tok, int col) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (8 * kPitch) + tok * kPitch + col];
+            return sum;
+        };
+        auto emit = [&](int tok, int col, float sum) {
             const int n = n_base + col;
             if (tok < M && n < N) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (8 * kPitch) + tok * kPitch + col];
                 const uint16_t bias_bits = has_bias ? __ldg(bias + n) : uint16_t(0);
                 c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16, has_bias, bias_bits);
             }
+        };
+        if (sp.ks == 1) {
+            for (int o = threadIdx.x; o < 8 * kCols; o += kSmThreads) emit(o / kCols, o % kCols, sum_of(o / kCols, o % kCols));
+            __syncthreads();
+        } else {
+            split_finish<8, kCols>(sp, group, slice, &last_flag, sum_of, emit);
         }
-        __syncthreads();
     }
+}
+
+struct StreamLaunch {
+    const void* a;
+    const uint8_t* w;
+    const float* scale;
+    const void* bias;
+    void* c;
+    int M, N, K;
+    long long ldc;
+    int out_mode, sms, ks;
+    void* workspace;
+    cudaStream_t stream;
+};
+
+// One launch path for every instantiation: dynamic shared memory opt-in once per device, programmatic dependent launch
+// allowed, `ks` CTAs per group of strips when the caller's workspace carries the cross-CTA reduction.
+template <typename Kernel>
+static cudaError_t launch_stream(Kernel kernel, int smem_bytes, int cols_per_item, int tokens_per_item, const StreamLaunch& L, bool* configured,
+                                 std::mutex& mu) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+            if (e != cudaSuccess) return e;
+            configured[dev] = true;
+        }
+    }
+    const int groups = (L.N + cols_per_item - 1) / cols_per_item;
+    const int items = groups * L.ks;
+    SplitArgs sp{L.ks, nullptr, nullptr};
+    if (L.ks > 1) {
+        sp.counters = reinterpret_cast<int*>(L.workspace);
+        sp.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(L.workspace) + kSmCounterBytes);
+    }
+    (void)tokens_per_item;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(items < L.sms ? items : L.sms), 1, 1);
+    cfg.blockDim = dim3(kSmThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cfg.stream = L.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint16_t*>(L.a), L.w, L.scale, reinterpret_cast<const uint16_t*>(L.bias),
+                              reinterpret_cast<uint16_t*>(L.c), L.M, L.N, L.K, L.ldc, L.out_mode, items, sp);
 }
 
 template <int P, int U>
-static cudaError_t launch_small8(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int M, int N, int K, long long ldc,
-                                 int out_bf16, int sms, cudaStream_t stream) {
-    auto kernel = small_m8_kernel<P, U>;
-    constexpr int kSmem = kSmWarps * 8 * (P * 16 + 1) * static_cast<int>(sizeof(float));
+static cudaError_t launch_small8(const StreamLaunch& L) {
     static std::mutex mu;
     static bool configured[64];
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-            if (e != cudaSuccess) return e;
-            configured[dev] = true;
-        }
-    }
-    const int items = (N + P * 16 - 1) / (P * 16);
-    const int grid = items < sms ? items : sms;
-    kernel<<<grid, kSmThreads, kSmem, stream>>>(reinterpret_cast<const uint16_t*>(a), w, scale, reinterpret_cast<const uint16_t*>(bias),
-                                                reinterpret_cast<uint16_t*>(c), M, N, K, ldc, out_bf16, items);
-    return cudaGetLastError();
+    return launch_stream(small_m8_kernel<P, U>, kSmWarps * 8 * (P * 16 + 1) * static_cast<int>(sizeof(float)), P * 16, 8, L, configured, mu);
 }
 
 template <int MT, int P, int U>
-static cudaError_t launch_small(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int M, int N, int K, long long ldc,
-                                int out_bf16, int sms, cudaStream_t stream) {
-    auto kernel = small_m_kernel<MT, P, U>;
-    constexpr int kSmem = kSmWarps * MT * 16 * (P * 8 + 1) * static_cast<int>(sizeof(float));
+static cudaError_t launch_small(const StreamLaunch& L) {
     static std::mutex mu;
     static bool configured[64];
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-            if (e != cudaSuccess) return e;
-            configured[dev] = true;
-        }
-    }
-    const int items = (N + P * 8 - 1) / (P * 8);
-    const int grid = items < sms ? items : sms;
-    kernel<<<grid, kSmThreads, kSmem, stream>>>(reinterpret_cast<const uint16_t*>(a), w, scale, reinterpret_cast<const uint16_t*>(bias),
-                                                reinterpret_cast<uint16_t*>(c), M, N, K, ldc, out_bf16, items);
-    return cudaGetLastError();
+    return launch_stream(small_m_kernel<MT, P, U>, kSmWarps * MT * 16 * (P * 8 + 1) * static_cast<int>(sizeof(float)), P * 8, MT * 16, L, configured, mu);
 }
 
-// Strips of 8 columns per work item, from the instantiated set: the one that wastes the fewest SM-rounds; among equals the
-// largest (token fragments are reused across the strips of an item).
-static int pick_strips(int N, int sms, int max_p, int strip_cols = 8) {
-    static const int kChoices[] = {16, 12, 10, 8, 6, 5, 4, 3, 2, 1};
+// How the weight is cut into CTA-sized pieces: P strips per work item (token fragments are reused across the strips of an
+// item) and ks K slices per item.  Cost model: rounds of CTAs over the SMs x k16-block-strips per CTA, plus a fixed
+// per-CTA cost (prologue, in-CTA reduction, and for a split the trip through the workspace) counted in the same unit.
+// Without a workspace ks stays 1.
+struct StreamPlan {
+    int p, ks;
+};
+static StreamPlan plan_stream(int N, int K, int sms, const int* p_choices, int n_choices, int strip_cols, int tokens, size_t ws_bytes) {
     const int strips = (N + strip_cols - 1) / strip_cols;
-    int best_p = 1;
-    double best_eff = -1.0;
-    for (int p : kChoices) {
-        if (p > max_p) continue;
-        const int items = (strips + p - 1) / p;
-        const int rounds = (items + sms - 1) / sms;
-        const double eff = static_cast<double>(strips) / (static_cast<double>(rounds) * sms * p);
-        if (eff > best_eff + 0.02) {
-            best_eff = eff;
-            best_p = p;
+    const int nkb = K / 16;
+    StreamPlan best{1, 1};
+    double best_cost = -1.0;
+    for (int i = 0; i < n_choices; ++i) {
+        const int p = p_choices[i];
+        const int groups = (strips + p - 1) / p;
+        for (int ks = 1; ks <= 8; ++ks) {
+            if (ks > 1) {
+                if (nkb / ks < 2 * kSmWarps) break;                                  // every warp keeps at least two k16-blocks
+                const size_t need = kSmCounterBytes + static_cast<size_t>(groups) * ks * tokens * p * strip_cols * sizeof(float);
+                if (need > ws_bytes || static_cast<size_t>(groups) * sizeof(int) > kSmCounterBytes) break;
+            }
+            const long long ctas = static_cast<long long>(groups) * ks;
+            const long long rounds = (ctas + sms - 1) / sms;
+            const double per_cta = static_cast<double>(p) * nkb / ks + 60.0 + (ks > 1 ? 40.0 : 0.0);
+            const double cost = rounds * per_cta;
+            if (best_cost < 0 || cost < best_cost * 0.98) {
+                best_cost = cost;
+                best = StreamPlan{p, ks};
+            }
         }
     }
-    return best_p;
+    return best;
 }
 
 #define FEATHER_SMALL_CASE(MT_, P_, U_) \
-    case P_: e = launch_small<MT_, P_, U_>(a, w, scale, bias, c, m, n, k, ldc, out_bf16, sms, stream); break;
+    case P_: e = launch_small<MT_, P_, U_>(L); break;
 #define FEATHER_SMALL8_CASE(P_, U_) \
-    case P_: e = launch_small8<P_, U_>(a, w, scale, bias, c, m, n, k, ldc, out_bf16, sms, stream); break;
+    case P_: e = launch_small8<P_, U_>(L); break;
+
+size_t small_m_workspace_bytes(int64_t M, int64_t N, int64_t K, int sms) {
+    // upper bound over the plans the launcher may pick: groups * ks * tokens * columns stays below 8 * tokens * N
+    (void)K;
+    (void)sms;
+    const int tokens = M <= 8 ? 8 : M <= 16 ? 16 : 32;
+    return kSmCounterBytes + static_cast<size_t>(8) * tokens * static_cast<size_t>(N + 256) * sizeof(float);
+}
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                   int output_dtype, int flip_final, int sms, cudaStream_t stream) {
-    // the kernels' `out_bf16` argument carries both bits of sm_finish's out_mode
-    const int out_bf16 = (output_dtype == FEATHER_OUT_BF16 ? 1 : 0) | (flip_final ? 2 : 0);
-    const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+                   int output_dtype, int flip_final, int sms, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    StreamLaunch L{a, w, scale, bias, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc,
+                   // the kernels' `out_bf16` argument carries both bits of sm_finish's out_mode
+                   (output_dtype == FEATHER_OUT_BF16 ? 1 : 0) | (flip_final ? 2 : 0), sms, 1, workspace, stream};
+    const size_t ws = (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) ? workspace_bytes : 0;
     cudaError_t e = cudaErrorInvalidValue;
     if (M <= 8) {
-        switch (pick_strips(n, sms, 8, 16)) {
+        static const int kP[] = {9, 8, 7, 6, 5, 4, 3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 9, 16, 8, ws);
+        L.ks = pl.ks;
+        switch (pl.p) {
+            FEATHER_SMALL8_CASE(9, 1)
             FEATHER_SMALL8_CASE(8, 1)
+            FEATHER_SMALL8_CASE(7, 1)
             FEATHER_SMALL8_CASE(6, 1)
             FEATHER_SMALL8_CASE(5, 2)
             FEATHER_SMALL8_CASE(4, 2)
@@ -349,10 +460,14 @@ int small_m_launch(const void* a, const uint8_t* w, const float* scale, const vo
             default: break;
         }
     } else if (M <= 16) {
-        switch (pick_strips(n, sms, 16)) {
+        static const int kP[] = {16, 12, 10, 9, 8, 6, 5, 4, 3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 11, 8, 16, ws);
+        L.ks = pl.ks;
+        switch (pl.p) {
             FEATHER_SMALL_CASE(1, 16, 1)
             FEATHER_SMALL_CASE(1, 12, 2)
             FEATHER_SMALL_CASE(1, 10, 2)
+            FEATHER_SMALL_CASE(1, 9, 2)
             FEATHER_SMALL_CASE(1, 8, 2)
             FEATHER_SMALL_CASE(1, 6, 4)
             FEATHER_SMALL_CASE(1, 5, 4)
@@ -363,7 +478,10 @@ int small_m_launch(const void* a, const uint8_t* w, const float* scale, const vo
             default: break;
         }
     } else {   // two token tiles: twice the accumulators, so at most 8 strips per item
-        switch (pick_strips(n, sms, 8)) {
+        static const int kP[] = {8, 6, 5, 4, 3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 7, 8, 32, ws);
+        L.ks = pl.ks;
+        switch (pl.p) {
             FEATHER_SMALL_CASE(2, 8, 1)
             FEATHER_SMALL_CASE(2, 6, 1)
             FEATHER_SMALL_CASE(2, 5, 2)

@@ -160,7 +160,8 @@ FEATHER_API int feather_reduce_partials(const void* partials, int n_src, int64_t
                                         int64_t ld_res, void* const* dst_list_host, int n_dst, int64_t ld_dst, int dtype,
                                         feather_stream_t stream);
 
-/* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K).  Pass the same
+/* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K; for the streaming kernel an upper bound of
+ * what a K split across CTAs may use - with less, or none, it splits less, or not at all).  Pass the same
  * `variant` (or NULL) as to feather_scaled_mm_ex.  The reference's shipped kernel never splits K (README.md:31
  * names an unshipped split-k branch), so its launcher has no scratch argument (kernel/hip/hip_kernel.cu:564-582). */
 FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant);
@@ -174,8 +175,8 @@ FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64
  *   - A K split the library chooses itself (variant NULL or split_k 0) is shrunk to what the array holds, exactly as
  *     feather_scaled_mm_ex shrinks it to the caller's workspace.  Only a variant that pins a larger split_k is rejected,
  *     with FEATHER_ERR_WORKSPACE (the message says how much is needed): pass a smaller split_k, or use feather_scaled_mm_ex.
- *   - Up to 16 tokens the library's own choice is the register-streaming kernel, which uses no scratch; such calls (and
- *     variant.kernel = FEATHER_KERNEL_STREAM) never touch the array.
+ *   - Up to 16 tokens the library's own choice is the register-streaming kernel; it uses the array only for the counters
+ *     and partial sums of a K split across CTAs, which it chooses when the weight's columns alone cannot fill the SMs.
  *   - The call allocates and frees nothing.  The first call on each device that needs the array looks its device address
  *     up (cudaGetSymbolAddress, with that device current) and keeps it; make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps what the previous call left there; the call clears the tile

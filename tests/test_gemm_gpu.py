@@ -151,6 +151,22 @@ def test_streaming_kernel_against_oracle(native, cuda_dev, M, N, K, out_dtype, b
     assert_gemm_close(tmem, ref, out_dtype, fo, f"tensor-memory kernel {(M, N, K)}", bias=b)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 5120, 13824), (8, 5120, 4096), (16, 5120, 13824), (12, 2048, 8192), (24, 1024, 4096)])
+def test_streaming_kernel_k_split_across_ctas(native, cuda_dev, M, N, K):
+    """Few weight columns and a long K: the streaming kernel shares a group of strips between several CTAs, each over a slice
+    of K, through the workspace (partials added in slice order by the last CTA to arrive).  Against the oracle, bitwise
+    repeatable, equal to the forced choice, and the tile counters are back at zero."""
+    a, bq, s, b = _synthetic(M, N, K, "bf16", seed=M + N + K)
+    ref = fo.scaled_mm(a, bq, s, b, "bf16", product="fp32")
+    stream = (0, 0, 0, 0, 0, native.KERNEL_STREAM)
+    runs = [_run(native, cuda_dev, a, bq, s, b, "bf16", stream) for _ in range(3)]
+    assert_gemm_close(runs[0], ref, "bf16", fo, f"{(M, N, K)}", bias=b)
+    assert all(np.array_equal(r, runs[0]) for r in runs[1:])
+    ws = native.workspace_for(cuda_dev)
+    assert int(ws[:65536].view(torch.int32).abs().sum().item()) == 0
+    assert native.workspace_bytes(M, N, K) <= ws.numel()
+
+
 def test_streaming_kernel_rejects_many_tokens(native, cuda_dev):
     a, bq, s, b = _synthetic(40, 64, 64, "bf16", seed=2)
     with pytest.raises(native.FeatherNativeError, match="at most 32 tokens"):
