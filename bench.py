@@ -594,6 +594,7 @@ def run_smallm(args, native, dev, Ms=(1, 8, 16, 64, 128), steps=None):
     peaks = load_peaks()
     steps = steps if steps is not None else args.steps
     rows = []
+    side = torch.cuda.Stream()          # one capture stream for every graph: the split-K workspace belongs to the (device, stream) pair
     for K, N in ((5120, 13824), (13824, 5120)):
         g = torch.Generator(device=dev).manual_seed(0)
         w = torch.randn((N, K), generator=g, device=dev) / K ** 0.5
@@ -621,7 +622,7 @@ def run_smallm(args, native, dev, Ms=(1, 8, 16, 64, 128), steps=None):
             torch.cuda.synchronize()
             us_eager = e0.elapsed_time(e1) * 1e3 / (steps * len(copies))
             # the same launches replayed from a CUDA graph: kernel time without the host's per-call cost
-            graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
             with torch.cuda.stream(side):
                 sweep()
                 torch.cuda.synchronize()

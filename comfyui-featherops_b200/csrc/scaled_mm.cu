@@ -1183,7 +1183,7 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     attr[0].val.clusterDim.z = 1;
     // the CTAs may become resident and set up while the previous kernel on the stream drains; see pdl_wait_for_previous_kernel
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].val.programmaticStreamSerializationAllowed = getenv("FEATHER_NO_PDL") == nullptr ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, p);

@@ -182,7 +182,9 @@ class _OnDevice:
 
 
 _scratch_ptrs = {}
-_MAX_STREAM_WORKSPACES = 8    # per process: 64 MiB each, so side streams beyond this run unsplit instead of allocating more
+# torch hands out its side streams from a fixed pool per device, so the number of distinct streams is bounded; a stream beyond
+# this many gets no workspace and its GEMMs run without a K split (correct, a little slower at small token counts)
+_MAX_STREAM_WORKSPACES = 72
 
 
 def _scratch_ptrs_for(dev, stream):
@@ -192,7 +194,8 @@ def _scratch_ptrs_for(dev, stream):
     Split-K launches that may overlap on the GPU need separate workspaces (tile counters and fp32 partials live there), so
     the workspace belongs to the (device, stream) pair, not to the device: two threads or side streams doing split-K GEMMs
     on one GPU never share one.  After _MAX_STREAM_WORKSPACES distinct streams a further stream gets no workspace, which
-    makes the library choose a variant without a K split for it (correct, a little slower at small token counts).
+    makes the library choose a variant without a K split for it.  The first stream of a device gets _WORKSPACE_BYTES, every
+    further one a quarter of that (the library fits its K split to what it is given).
     """
     index = dev.index if dev.index is not None else torch.cuda.current_device()
     key = (index, stream)
@@ -202,7 +205,7 @@ def _scratch_ptrs_for(dev, stream):
         with _scratch_lock:
             n_ws = sum(1 for k in _workspaces if k[1] == index)
         if n_ws < _MAX_STREAM_WORKSPACES:
-            ws = workspace_for(dev, stream)
+            ws = workspace_for(dev, stream, nbytes=_WORKSPACE_BYTES if n_ws == 0 else _WORKSPACE_BYTES // 4)
             got = (index, ws.data_ptr(), ws.numel(), st.data_ptr())
         else:
             got = (index, None, 0, st.data_ptr())
@@ -228,7 +231,7 @@ _status_words = {}
 _amax_words = {}
 
 
-def workspace_for(device, stream=None):
+def workspace_for(device, stream=None, nbytes=None):
     """Zero-initialised split-K workspace for launches on `stream` of `device` (a raw cudaStream_t as an int; default: the
     current stream), allocated on first use through torch's allocator.
 
@@ -242,7 +245,7 @@ def workspace_for(device, stream=None):
     with _scratch_lock:
         ws = _workspaces.get(key)
         if ws is None:
-            ws = torch.zeros(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+            ws = torch.zeros(_WORKSPACE_BYTES if nbytes is None else nbytes, dtype=torch.uint8, device=device)
             # the zero fill ran on torch's current stream; the first GEMM may be enqueued on another one
             torch.cuda.current_stream(device).synchronize()
             _workspaces[key] = ws
