@@ -61,8 +61,8 @@ __host__ __device__ constexpr int pow2_at_least(int x) {
     return p;
 }
 
-// OB: staging buffers per epilogue group.  1 for an ordinary launch; 4 (a whole 256-token tile per CTA) when the blocks also go
-// to peer GPUs, so that NVLink takes its time over a tile while the tensor cores already run the next one.
+// OB: staging buffers per epilogue group.  1 for an ordinary launch; 2 when the blocks also go to peer GPUs, so that a block
+// can be staged while NVLink is still taking the previous one.
 template <int TN, int CG, int OB = 1>
 struct Cfg {
     static_assert(TN == 16 || TN == 32 || TN == 64 || TN == 128 || TN == 192 || TN == 256, "tokens tile");
@@ -86,11 +86,12 @@ struct Cfg {
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kOutRows = TN < 32 ? TN : 32;                   // token rows per output staging buffer
     static constexpr int kOutBufBytes = kOutRows * kBW * 2;              // [2 tiles][rows][64 n] 16-bit
-    // Staging buffers per epilogue group.  On one GPU two (a block is staged while TMA still reads the previous one)
-    // measured no faster at 256-token tiles than one: the 16 KB come out of the weight-byte ring, which then runs a stage
-    // short.  With peer destinations the picture changes: a tile's blocks leave at NVLink speed (3 or 7 copies of each),
-    // which takes about as long as the tile's MMAs, and with one buffer the accumulator is held until they have left.
-    static_assert(OB == 1 || (OB == 4 && TN == 256), "staging ring depth");
+    // Staging buffers per epilogue group.  The memory comes out of the weight-byte ring, and that ring's depth matters more
+    // than it looks: on one GPU the Wan ffn shapes ran at 1507 / 1540 TFLOP/s with five weight stages (one buffer), 1412 / 1370
+    // with four (two buffers), and 912 / 762 with two (four buffers, a whole tile).  So an ordinary launch stages through one
+    // buffer.  With peer destinations a tile's blocks leave at NVLink speed, and two buffers measured best (2 GPUs: 2754
+    // TFLOP/s against 2699 with one and 1966 with four).
+    static_assert(OB == 1 || (OB == 2 && TN == 256), "staging ring depth");
     static constexpr int kOutBufs = OB;
     static constexpr int kOutBytes = 2 * kOutBufs * kOutBufBytes;
     static constexpr int kSmemBudget = 227 * 1024 - 1024 /*alignment slack*/ - kBarrierBytes - kOutBytes;
@@ -1193,8 +1194,8 @@ template <int TN>
 static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p,
                              int grid, cudaStream_t s) {
     if constexpr (TN == 256) {
-        // pairs of 256-token tiles whose blocks also cross NVLink: a staging ring that holds a whole tile
-        if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 4>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2, 4>(tw, ta, tc, p, grid, s);
+        // pairs of 256-token tiles whose blocks also cross NVLink: two staging buffers per epilogue group
+        if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 2>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2, 2>(tw, ta, tc, p, grid, s);
     }
     if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
     return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
@@ -1332,9 +1333,9 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     p.tma_store = tma_store ? 1 : 0;
     p.n_dst = 1 + n_extra;
     p.scatter_rows = static_cast<int>(scatter_rows);
-    // variant.staging: 0 = a tile-deep staging ring whenever blocks go to more than one buffer, 1 = never, 2 = always
+    // variant.staging: 0 = two staging buffers per group whenever blocks go to more than one buffer, 1 = never, 2 = always
     const int staging_mode = variant ? variant->staging : 0;
-    if (staging_mode < 0 || staging_mode > 2) return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.staging must be 0 (auto), 1 (one buffer) or 2 (a whole tile)");
+    if (staging_mode < 0 || staging_mode > 2) return set_error(FEATHER_ERR_BAD_ARGUMENT, "variant.staging must be 0 (auto), 1 (one buffer) or 2 (two buffers)");
     const bool deep_staging = tma_store && (staging_mode == 2 || (staging_mode == 0 && n_extra > 0));
     p.scale = scale;
     p.bias = bias;

@@ -7,8 +7,8 @@ ColumnShardedLinear   rank r keeps the weight columns [r*N/g, (r+1)*N/g) (dim 1)
                       same order on any number of ranks: the result is bitwise the single-GPU result.  Exchanges:
     "peer_store"      fused into the GEMM.  The output is an [M, N] buffer in symmetric memory on every rank; the kernel's
                       epilogue TMA-stores each finished block into its column range of ALL ranks' buffers while the tensor
-                      cores run the next tile (a staging ring that holds a whole tile lets NVLink take as long as the tile's
-                      MMAs).  Outputs are double-buffered per (M, dtype), so ONE cross-rank barrier per call is enough, the one
+                      cores run the next tile (two staging buffers per epilogue group, so a block is staged while NVLink
+                      still takes the previous one).  Outputs are double-buffered per (M, dtype), so ONE cross-rank barrier per call is enough, the one
                       after the launch ("all blocks have landed"): a rank reaches the barrier of call n only after its own
                       stream has run everything that read the output of call n-1, so once call n's barrier has passed, nobody
                       still reads the buffer that call n+1 overwrites.

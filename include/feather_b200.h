@@ -60,8 +60,8 @@ enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
  *   max_ctas    : cap on the persistent grid (0 = number of SMs)
  *   kernel      : 0 = choose from the shape (streaming up to 16 tokens); 1 = the tensor-memory (tcgen05) kernel; 2 = the
  *                 register-streaming kernel, at most 32 tokens (needs no workspace, ignores the other fields)
- *   staging     : output staging of 256-token pair tiles: 0 = choose (a ring that holds a whole tile when blocks also go to
- *                 peer GPUs, one buffer otherwise), 1 = one buffer, 2 = the whole-tile ring
+ *   staging     : output staging of 256-token pair tiles: 0 = choose (two buffers per epilogue group when blocks also go to
+ *                 peer GPUs, one otherwise), 1 = one buffer, 2 = two buffers
  */
 enum { FEATHER_KERNEL_AUTO = 0, FEATHER_KERNEL_TMEM = 1, FEATHER_KERNEL_STREAM = 2 };
 typedef struct feather_mm_variant {

@@ -102,7 +102,7 @@ VARIANT_CASES = [
     (90, 250, 256, "fp16", (128, 1, 1, 2, 0), True, True),           # N % 8 != 0: rows not 16-byte aligned, plain-store epilogue
     (700, 600, 2048, "fp16", (128, 2, 1, 1, 8), True, True),        # pairs, N not a multiple of 256
     (64, 512, 4096, "fp16", (64, 2, 4, 2, 0), True, True),          # pairs + split-K
-    (3000, 1024, 512, "bf16", (256, 2, 1, 2, 8, 0, 2), True, True),  # tile-deep staging ring: 4 CTA pairs walk 48 tiles, ragged last token tile
+    (3000, 1024, 512, "bf16", (256, 2, 1, 2, 8, 0, 2), True, True),  # two staging buffers per epilogue group: 4 CTA pairs walk 48 tiles, ragged last token tile
     (1500, 520, 256, "fp16", (256, 2, 1, 1, 4, 0, 2), True, True),  # the same with one transform group, N not a multiple of the tile
     (16, 5120, 1024, "bf16", None, True, True),                     # library-chosen variant
     (300, 1024, 1024, "bf16", None, False, True),
@@ -352,6 +352,25 @@ def test_multi_destination_epilogue_on_one_gpu(native, cuda_dev):
         odd = [torch.empty((300, 250), dtype=torch.bfloat16, device=cuda_dev) for _ in range(2)]
         a2, bq2, s2, _ = _synthetic(300, 250, 64, "bf16", seed=1, bias=False)
         native.scaled_mm_multi_into(to_torch(a2, "fp16", cuda_dev), to_torch(bq2, "e5m2", cuda_dev), None, None, odd)
+
+
+@pytest.mark.parametrize("variant", [(256, 2, 1, 2, 8), (256, 2, 1, 1, 6), None])
+def test_many_tiles_to_several_destinations_on_one_gpu(native, cuda_dev, variant):
+    """256-token pair tiles stored to several destinations (here all on one GPU; across GPUs those stores cross NVLink): a few
+    CTA pairs walk many tiles through the two staging buffers of each epilogue group, the last token tile and the last column
+    tile are ragged; every buffer must hold the single-destination result bit for bit and nothing outside its column range."""
+    a, bq, s, b = _synthetic(3000, 904, 512, "bf16", seed=77)
+    single = _run(native, cuda_dev, a, bq, s, b, "bf16", (256, 2, 1, 2, 0))
+    A, B = to_torch(a, "fp16", cuda_dev), to_torch(bq, "e5m2", cuda_dev)
+    S = torch.tensor([float(s)], dtype=torch.float32, device=cuda_dev)
+    Bi = to_torch(b, "bf16", cuda_dev)
+    wide = [torch.full((3000, 1800), 7.0, dtype=torch.bfloat16, device=cuda_dev) for _ in range(4)]
+    for _ in range(2):
+        native.scaled_mm_multi_into(A, B, S, Bi, [w[:, 448:448 + 904] for w in wide], variant=native.make_variant(*variant) if variant else None)
+    native.check_device_status(cuda_dev)
+    for w in wide:
+        assert np.array_equal(from_torch(w[:, 448:448 + 904]), single)
+        assert bool((w[:, :448] == 7.0).all()) and bool((w[:, 448 + 904:] == 7.0).all())
 
 
 @pytest.mark.parametrize("K,N", [(5120, 13824), (13824, 5120), (5120, 5120)])

@@ -58,7 +58,7 @@ def _worker(rank, world, port, tmpdir):
             out = lin(a, torch.bfloat16)
             torch.cuda.synchronize()
             check(f"column {exchange} call {call}", out.shape == (M, N) and torch.equal(out.view(torch.int16), full.view(torch.int16)))
-    # 256-token pair tiles with the tile-deep staging ring (what the benchmark shapes use), ragged last tile
+    # 256-token pair tiles with two staging buffers per epilogue group (what the benchmark shapes use), ragged last tile
     M3 = 8192 + 136                                           # 99 pair tiles per rank: some CTA pairs run two tiles through the ring
     a3 = torch.randn((M3, K), generator=g, device=dev).to(torch.float16)
     full3 = torch.empty((M3, N), dtype=torch.bfloat16, device=dev)
