@@ -15,8 +15,8 @@ from comfy.ops import cast_bias_weight, manual_cast, run_every_op, uncast_bias_w
 from torch import nn
 
 from ..kernel.convert import bf16_to_fp16
-from ..kernel.hip.hip_kernel import scaled_mm_b200
-from .lora import apply_lora_patches
+from ..kernel.hip.hip_kernel import scaled_mm_b200, scaled_mm_lora
+from .lora import apply_lora_patches, fused_lora_operands
 from .quant import get_feather_plain_tensors, is_feather_quantized_weight, make_feather_quantized_weight, quantize_feather_weight
 
 
@@ -80,7 +80,7 @@ def feather_ops(out_dtype=torch.bfloat16, excluded_names=()):
                 assert inplace_update is False
                 self.weight = nn.Parameter(weight, requires_grad=False)
 
-            def _forward_quantized(self, x):
+            def _forward_quantized(self, x, lora_functions=()):
                 """x [M,K] any float dtype -> [M,N] in x's dtype, through the fp16/bf16 x e5m2 kernel.
 
                 The reference casts the activations to fp16, runs the op and casts the result back (ops.py:88,103).  Here
@@ -107,11 +107,17 @@ def feather_ops(out_dtype=torch.bfloat16, excluded_names=()):
                     weight, bias, offload_stream = cast_bias_weight(self, x, dtype=self.weight.dtype, bias_dtype=bias_dtype, offloadable=True)
                     qdata, scale = get_feather_plain_tensors(weight)
                     scale = scale.to(device=x.device, dtype=torch.float32)
-                    y = scaled_mm_b200(x, qdata, scale, bias, out_dtype=self.out_dtype, final_dtype=final_dtype)
+                    # un-merged LoRA patches: folded into this GEMM's accumulator when that pays (see lora.py), else added afterwards
+                    fused = fused_lora_operands(x, lora_functions, scale) if lora_functions else None
+                    if fused is not None:
+                        y = scaled_mm_lora(x, qdata, scale, bias, self.out_dtype, final_dtype, *fused)
+                    else:
+                        y = scaled_mm_b200(x, qdata, scale, bias, out_dtype=self.out_dtype, final_dtype=final_dtype)
                     uncast_bias_weight(self, weight, bias, offload_stream)
                 finally:
                     self.weight_function = saved_weight_function
-                return y if y.dtype == dtype_orig else y.to(dtype_orig)
+                y = y if y.dtype == dtype_orig else y.to(dtype_orig)
+                return y, fused is not None
 
             def forward(self, input: torch.Tensor) -> torch.Tensor:
                 x = input
@@ -129,8 +135,9 @@ def feather_ops(out_dtype=torch.bfloat16, excluded_names=()):
                 if x.shape[0] == 0:
                     return x.new_empty(*batch_shape, self.out_features)
 
-                y = self._forward_quantized(x)
-                y = apply_lora_patches(x, y, self.weight_function)
+                y, lora_done = self._forward_quantized(x, self.weight_function)
+                if not lora_done:
+                    y = apply_lora_patches(x, y, self.weight_function)
                 return y.view(*batch_shape, y.shape[-1])
 
     return FeatherOps

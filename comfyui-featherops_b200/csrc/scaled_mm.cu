@@ -125,6 +125,10 @@ struct MmParams {
     int a_bf16;    // 1: the activations are bf16 (the weights are upcast to bf16 too, and the MMA runs bf16 x bf16)
     int w_e4m3;    // 1: the weight bytes are fp8e4m3fn; they are upcast to 1/256 of their value and scale_mul puts the factor back
     float scale_mul;
+    // Un-merged LoRA folded into the accumulator: after the weight's k-blocks every tile runs lora_blocks more blocks of 64
+    // "k" each, whose token operand is T' [M, R] (the down-projected activations) and whose weight operand is B' [R/8, N, 8],
+    // both already in the 16-bit format of the MMA (no upcast), scaled so that T' B'^T = (x A^T) B^T * strength / scale.
+    int lora_blocks;
     int a3d;       // 1: the token tensor map is the 3-D form (64 k, M, K/64): one copy per k-block
     int c3d;       // 1: the output tensor maps are the 3-D form (64 n, M, N/64): one store per staged block and destination
     int tma_store; // 1: output rows are 16-byte aligned, the epilogue stores tiles with TMA; 0: plain 2-byte stores
@@ -141,9 +145,16 @@ constexpr int kMaxDst = 8;
 struct OutMaps {
     CUtensorMap m[kMaxDst];
 };
+// Tensor maps of the low-rank term: t = T' as (R, M) 16-bit with a (64, tokens per CTA) box in the 128-byte swizzle (one token
+// sub-tile); b = B' as 8-byte elements (2N, R/8) with the weight map's (256, 8) box, which lands as [8][128 n][16 B] = one
+// weight stage holding 64 ranks of 16-bit values.
+struct LoraMaps {
+    CUtensorMap t, b;
+};
 
 struct Unit {
     int tile, split, n0, tok0, kb_begin, kb_count;
+    int kb_total;   // kb_count plus the low-rank blocks that follow the weight's k-blocks (0 without a LoRA term)
 };
 
 template <int TN, int CG>
@@ -166,6 +177,7 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
     const int rem = p.total_kb - base * p.splits;
     w.kb_begin = w.split * base + (w.split < rem ? w.split : rem);
     w.kb_count = base + (w.split < rem ? 1 : 0);
+    w.kb_total = w.kb_count + p.lora_blocks;
     return w;
 }
 
@@ -252,7 +264,7 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
 template <int TN, int CG, int TG, int OB = 1>
 __global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ OutMaps tmap_c, const MmParams p) {
+                 const __grid_constant__ OutMaps tmap_c, const __grid_constant__ LoraMaps tmap_l, const MmParams p) {
     using C = Cfg<TN, CG, OB>;
     constexpr int kStages = C::kAStages;                                  // operand ring depth (token tile + upcast weights per slot)
     constexpr int kWStages = C::kWStages;
@@ -361,7 +373,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
                     const Unit w = decode_unit<TN, CG>(p, u);
                     int kb = w.kb_begin;
-                    for (int i = 0; i < w.kb_count; ++i, ++kb, ++it) {
+                    for (int i = 0; i < w.kb_total; ++i, ++kb, ++it) {
+                        const bool low_rank = i >= w.kb_count;                       // block e = i - kb_count of the LoRA term
+                        const int e = i - w.kb_count;
                         tw.start();
                         const bool free_ok = mbar_wait_warp(bar_free + 8 * s, ph ^ 1u, abort_flag, lane);
                         tw.stop(st_wait);
@@ -374,15 +388,24 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                             // nothing to issue
                         } else if constexpr (kWeights) {
                             mbar_arrive_expect_tx(bar_wfull + 8 * s, kWStageBytes);
-                            tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, w.n0 * 2 + n_coord, kb * kKSteps);
+                            if (low_rank)
+                                tma_load_2d(smem_w + s * kWStageBytes, &tmap_l.b, bar_wfull + 8 * s, w.n0 * 2 + n_coord, e * 8);
+                            else
+                                tma_load_2d(smem_w + s * kWStageBytes, &tmap_w, bar_wfull + 8 * s, w.n0 * 2 + n_coord, kb * kKSteps);
                         } else {
                             const uint32_t bar = kPair ? mapa_u32(bar_full + 8 * s, 0) : bar_full + 8 * s;
                             const uint32_t dst = smem_a + s * C::kAStageBytes;
+                            const uint32_t tx_bytes = low_rank ? C::kASubBytes : C::kAStageBytes;     // a low-rank block is one sub-tile
                             if constexpr (!kPair)
-                                mbar_arrive_expect_tx(bar, C::kAStageBytes);
+                                mbar_arrive_expect_tx(bar, tx_bytes);
                             else
-                                mbar_arrive_expect_tx_cluster(bar, C::kAStageBytes);
-                            if (p.a3d) {
+                                mbar_arrive_expect_tx_cluster(bar, tx_bytes);
+                            if (low_rank) {
+                                if constexpr (!kPair)
+                                    tma_load_2d(dst, &tmap_l.t, bar, e * kSubK, w.tok0);
+                                else
+                                    tma_load_2d_pair(dst, &tmap_l.t, bar, e * kSubK, w.tok0 + tok_off);
+                            } else if (p.a3d) {
                                 if constexpr (!kPair)
                                     tma_load_3d(dst, &tmap_a, bar, 0, w.tok0, kb * kSubTiles);
                                 else
@@ -470,7 +493,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (a * kIssuers + issuer) * TN;
                 uint32_t accumulate = 0;                                          // this issuer's first MMA of a tile overwrites its accumulator
-                for (int i = 0; i < w.kb_count; ++i) {
+                for (int i = 0; i < w.kb_total; ++i) {
                     if (kIssuers == 2 && (static_cast<uint32_t>(i) & 1u) != issuer) {
                         advance(s, ph);
                         continue;
@@ -492,17 +515,20 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     uint32_t sn = s, phn = ph;
 #pragma unroll
                     for (int j = 0; j < kIssuers; ++j) advance(sn, phn);
-                    peeked = (i + kIssuers < w.kb_count) && mbar_test_wait(bar_full + 8 * sn, phn);
+                    peeked = (i + kIssuers < w.kb_total) && mbar_test_wait(bar_full + 8 * sn, phn);
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_wring + s * kTColsPerStage;
                     const uint64_t b_stage = desc0 + static_cast<uint64_t>(s * (C::kAStageBytes >> 4));
+                    const int sub_tiles = i >= w.kb_count ? 1 : kSubTiles;              // a low-rank block holds 64 k: one sub-tile
 #pragma unroll
                     for (int sub = 0; sub < kSubTiles; ++sub) {
+                        if (sub < sub_tiles) {
 #pragma unroll
-                        for (int ks = 0; ks < kSubK / 16; ++ks) {
-                            // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
-                            umma_f16_ts<CG>(d_tmem, a_tmem + (sub * (kSubK / 16) + ks) * 8,
-                                            b_stage + static_cast<uint64_t>(sub * (C::kASubBytes >> 4) + ks * 2), idesc, (sub | ks) != 0 ? 1u : accumulate);
+                            for (int ks = 0; ks < kSubK / 16; ++ks) {
+                                // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
+                                umma_f16_ts<CG>(d_tmem, a_tmem + (sub * (kSubK / 16) + ks) * 8,
+                                                b_stage + static_cast<uint64_t>(sub * (C::kASubBytes >> 4) + ks * 2), idesc, (sub | ks) != 0 ? 1u : accumulate);
+                            }
                         }
                     }
                     if constexpr (!kPair)
@@ -558,8 +584,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tt.start();
         for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
             const Unit w = decode_unit<TN, CG>(p, u);
-            for (int i = 0; i < w.kb_count; ++i) {
+            for (int i = 0; i < w.kb_total; ++i) {
                 const uint32_t s = ws, ph = wph, t = os, tph = oph;
+                const bool low_rank = i >= w.kb_count;
                 const bool mine = turn == g;
                 if (++ws == kWStages) {
                     ws = 0;
@@ -592,7 +619,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                      : "=r"(x[j][0]), "=r"(x[j][1]), "=r"(x[j][2]), "=r"(x[j][3])
                                      : "r"(src + j * (kBW * 16)));
-                    if (up_mode == 0) {
+                    if (low_rank) {
+                        // B' is already in the MMA's 16-bit format: 16 bytes are 8 ranks = 4 tensor-memory columns, no upcast
+#pragma unroll
+                        for (int j = 0; j < kKSteps; ++j) tmem_st_32x32b_x4(dst + j * 4, x[j]);
+                    } else if (up_mode == 0) {
 #pragma unroll
                         for (int j = 0; j < kKSteps; ++j) {
                             uint32_t v[8];
@@ -684,7 +715,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t src = tmem_base + t_lane + a * (kIssuers * TN);
             // With two issuers the tile's sum is split over two accumulators (even / odd k-blocks); a tile of one k-block has
             // nothing in the second.
-            const bool two_sums = kIssuers == 2 && w.kb_count >= 2;
+            const bool two_sums = kIssuers == 2 && w.kb_total >= 2;
             // 16 accumulator columns starting at column c0 -> registers (fp32 bit patterns), both partial sums added.
             auto load_sum16 = [&](int c0, uint32_t (&v)[16]) {
                 tmem_ld_32x32b_x16(src + c0, v);
@@ -1155,7 +1186,7 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
 }
 
 template <int TN, int CG, int TG, int OB = 1>
-static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p, int grid,
+static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl, const MmParams& p, int grid,
                                   cudaStream_t stream) {
     using C = Cfg<TN, CG, OB>;
     auto kernel = scaled_mm_kernel<TN, CG, TG, OB>;
@@ -1187,18 +1218,18 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     attr[1].val.programmaticStreamSerializationAllowed = getenv("FEATHER_NO_PDL") == nullptr ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, p);
+    return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, tl, p);
 }
 
 template <int TN>
-static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const MmParams& p,
-                             int grid, cudaStream_t s) {
+static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl,
+                             const MmParams& p, int grid, cudaStream_t s) {
     if constexpr (TN == 256) {
         // pairs of 256-token tiles whose blocks also cross NVLink: two staging buffers per epilogue group
-        if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 2>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2, 2>(tw, ta, tc, p, grid, s);
+        if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 2>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2, 2>(tw, ta, tc, tl, p, grid, s);
     }
-    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, p, grid, s);
-    return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, p, grid, s);
+    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, tl, p, grid, s);
+    return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, tl, p, grid, s);
 }
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
@@ -1210,6 +1241,10 @@ struct Types {
     bool a_bf16 = false;     // activations are bf16
     bool w_e4m3 = false;     // weights are fp8e4m3fn
     int final_dtype = -1;    // dtype stored (FEATHER_OUT_*); -1: the output dtype itself
+    // un-merged LoRA term folded into the accumulator (null: none): t = T' [M, R], lb = B' [R/8, N, 8], both in the activations' dtype
+    const void* lora_t = nullptr;
+    const void* lora_b = nullptr;
+    int64_t lora_rank = 0;
 };
 
 // Bandwidth-bound end (at most 16 tokens, or on request): the register-streaming kernel, unless the caller pinned a
@@ -1254,12 +1289,28 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         return set_error(FEATHER_ERR_BAD_ARGUMENT, "final_dtype must be -1 (same as output_dtype), 0 (fp16) or 1 (bf16)");
     const int flip_final = (types.final_dtype != -1 && types.final_dtype != output_dtype) ? 1 : 0;
     // the streaming kernel multiplies fp16 activations by e5m2 weights only; the other operand types take the tensor-memory kernel
-    const bool plain_operands = !types.a_bf16 && !types.w_e4m3;
+    const bool lora = types.lora_t != nullptr || types.lora_b != nullptr || types.lora_rank != 0;
+    if (lora) {
+        if (types.lora_t == nullptr || types.lora_b == nullptr || types.lora_rank <= 0 || types.lora_rank % kSubK != 0 || types.lora_rank > 4096)
+            return set_error(FEATHER_ERR_BAD_ARGUMENT, "LoRA term: t and lb must not be null and the rank must be a positive multiple of %d (pad with zeros)", kSubK);
+        if ((reinterpret_cast<uintptr_t>(types.lora_t) & 15u) != 0 || (reinterpret_cast<uintptr_t>(types.lora_b) & 15u) != 0)
+            return set_error(FEATHER_ERR_BAD_ARGUMENT, "LoRA term: t and lb must be 16-byte aligned");
+        if (n_extra != 0 || scatter_rows != 0) return set_error(FEATHER_ERR_UNSUPPORTED, "the LoRA term is not combined with sharded outputs");
+    }
+    const bool plain_operands = !types.a_bf16 && !types.w_e4m3 && !lora;
     if (plain_operands && takes_streaming_kernel(variant, M, n_extra))
         return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, flip_final, sms, workspace, workspace_bytes, stream);
     if (which == FEATHER_KERNEL_STREAM)
         return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer and takes fp16 activations and e5m2 weights");
     Plan pl;
+    feather_mm_variant lora_variant{};
+    if (lora) {
+        // the low-rank blocks follow the weight's k-blocks of a tile, so the tile's K is not split across work units
+        if (variant) lora_variant = *variant;
+        if (lora_variant.split_k > 1) return set_error(FEATHER_ERR_UNSUPPORTED, "the LoRA term needs a variant without a K split");
+        lora_variant.split_k = 1;
+        variant = &lora_variant;
+    }
     if (!make_plan(M, N, K, variant, workspace ? workspace_bytes : 0, true, sms, &pl))
         return set_error(FEATHER_ERR_UNSUPPORTED, "unsupported kernel variant");
     if (pl.splits > 1) {
@@ -1327,7 +1378,20 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         }
     }
 
+    LoraMaps tmap_l;
+    memset(&tmap_l, 0, sizeof(tmap_l));
+    if (lora) {
+        const uint64_t R = static_cast<uint64_t>(types.lora_rank);
+        CUresult r = cached_tmap(encode, &tmap_l.t, 5, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, types.lora_t, R, static_cast<uint64_t>(M), R * 2, kSubK,
+                                 static_cast<uint32_t>(pl.tn / pl.cg), CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(LoRA T) failed with CUresult %d", static_cast<int>(r));
+        r = cached_tmap(encode, &tmap_l.b, 6, CU_TENSOR_MAP_DATA_TYPE_UINT64, types.lora_b, static_cast<uint64_t>(N) * 2, R / 8, static_cast<uint64_t>(N) * 16,
+                        kBW * 2, kKSteps, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (r != CUDA_SUCCESS) return set_error(FEATHER_ERR_CUDA, "cuTensorMapEncodeTiled(LoRA B) failed with CUresult %d", static_cast<int>(r));
+    }
+
     MmParams p{};
+    p.lora_blocks = lora ? static_cast<int>(types.lora_rank / kSubK) : 0;
     p.a3d = a3d ? 1 : 0;
     p.c3d = c3d ? 1 : 0;
     p.tma_store = tma_store ? 1 : 0;
@@ -1370,12 +1434,12 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
 
     cudaError_t e = cudaErrorInvalidValue;
     switch (pl.tn) {
-        case 16: e = launch_tn<16>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 32: e = launch_tn<32>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 64: e = launch_tn<64>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 128: e = launch_tn<128>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 192: e = launch_tn<192>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
-        case 256: e = launch_tn<256>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, p, grid, stream); break;
+        case 16: e = launch_tn<16>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 32: e = launch_tn<32>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 64: e = launch_tn<64>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 128: e = launch_tn<128>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 192: e = launch_tn<192>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 256: e = launch_tn<256>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
         default: break;
     }
     if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "scaled_mm launch failed: %s", cudaGetErrorString(e));
@@ -1408,6 +1472,21 @@ extern "C" int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_t
     t.final_dtype = final_dtype;
     return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, workspace, workspace_bytes, status_dev,
                           static_cast<cudaStream_t>(stream), nullptr, 0, 0, t);
+}
+
+extern "C" int feather_scaled_mm_lora(const void* a, int a_dtype, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c, int64_t M,
+                                      int64_t N, int64_t K, int64_t ldc, int output_dtype, int final_dtype, const void* t, const void* lb_prepacked,
+                                      int64_t rank, const feather_mm_variant* variant, int* status_dev, feather_stream_t stream) {
+    if (a_dtype != FEATHER_SRC_FP16 && a_dtype != FEATHER_SRC_BF16)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "a_dtype must be %d (bf16) or %d (fp16)", FEATHER_SRC_BF16, FEATHER_SRC_FP16);
+    Types ty;
+    ty.a_bf16 = a_dtype == FEATHER_SRC_BF16;
+    ty.final_dtype = final_dtype;
+    ty.lora_t = t;
+    ty.lora_b = lb_prepacked;
+    ty.lora_rank = rank;
+    return scaled_mm_impl(a, b_prepacked, scale, bias, c, M, N, K, ldc, output_dtype, variant, nullptr, 0, status_dev, static_cast<cudaStream_t>(stream),
+                          nullptr, 0, 0, ty);
 }
 
 extern "C" int feather_scaled_mm_multi(const void* a, const uint8_t* b_prepacked, const float* scale, const void* bias, void* const* c_list_host,

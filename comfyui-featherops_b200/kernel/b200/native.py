@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_choose",
     "feather_scaled_mm_static",
     "feather_scaled_mm_typed",
+    "feather_scaled_mm_lora",
     "feather_scaled_mm_multi",
     "feather_scaled_mm_scatter",
     "feather_reduce_partials",
@@ -100,6 +101,8 @@ def load_library():
         lib.feather_scaled_mm_multi.restype = ci
         lib.feather_scaled_mm_typed.argtypes = [vp, ci, vp, ci, vp, vp, vp, i64, i64, i64, i64, ci, ci, ctypes.POINTER(MMVariant), vp, sz, vp, vp]
         lib.feather_scaled_mm_typed.restype = ci
+        lib.feather_scaled_mm_lora.argtypes = [vp, ci, vp, vp, vp, vp, i64, i64, i64, i64, ci, ci, vp, vp, i64, ctypes.POINTER(MMVariant), vp, vp]
+        lib.feather_scaled_mm_lora.restype = ci
         lib.feather_scaled_mm_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, i64, ci, ctypes.POINTER(MMVariant), vp, vp]
         lib.feather_scaled_mm_scatter.restype = ci
         lib.feather_reduce_partials.argtypes = [vp, ci, i64, i64, vp, vp, i64, ctypes.POINTER(vp), ci, i64, ci, vp]
@@ -388,6 +391,32 @@ def scaled_mm_typed_into(a, b_prepacked, scale, bias, c, out_dtype=None, variant
         )
     if status != FEATHER_OK:
         _check(status, "feather_scaled_mm_typed")
+    return c
+
+
+def scaled_mm_lora_into(a, b_prepacked, scale, bias, c, t, lb_prepacked, out_dtype=None, variant=None):
+    """c = cast(cvt((a @ up(b) + t @ lb^T) * scale) + bias): the linear with an un-merged LoRA term folded into the accumulator.
+    t [M, R] and lb_prepacked [R/8, N, 8] have a's dtype (fp16 or bf16), R a multiple of 64; see `feather_scaled_mm_lora`."""
+    lib = load_library()
+    dev = _require_cuda(a, b_prepacked, scale, bias, c, t, lb_prepacked)
+    M, K = a.shape
+    N = b_prepacked.shape[1]
+    R = t.shape[1]
+    if t.shape != (M, R) or lb_prepacked.shape != (R // 8, N, 8) or t.dtype != a.dtype or lb_prepacked.dtype != a.dtype:
+        raise FeatherNativeError("LoRA term: t must be [M, R] and lb_prepacked [R/8, N, 8], both in the activations' dtype")
+    if not (t.is_contiguous() and lb_prepacked.is_contiguous()):
+        raise FeatherNativeError("LoRA term: t and lb_prepacked must be contiguous")
+    out_dtype = c.dtype if out_dtype is None else out_dtype
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = status_word_for(dev)
+    with _OnDevice(index):
+        status = lib.feather_scaled_mm_lora(
+            a.data_ptr(), _SRC_CODE[a.dtype], b_prepacked.data_ptr(), _addr(scale), _addr(bias), c.data_ptr(), M, N, K, c.stride(0),
+            _OUT_CODE[out_dtype], _OUT_CODE[c.dtype], t.data_ptr(), lb_prepacked.data_ptr(), R,
+            ctypes.byref(variant) if variant is not None else None, st.data_ptr(), _raw_stream(index),
+        )
+    if status != FEATHER_OK:
+        _check(status, "feather_scaled_mm_lora")
     return c
 
 

@@ -273,6 +273,19 @@ def scaled_mm_hip(
     return out
 
 
+def scaled_mm_lora(a, b_prepacked, scale, bias, out_dtype, final_dtype, t, lb_prepacked):
+    """`scaled_mm_b200` with an un-merged LoRA term folded into the accumulator: returns
+    cast(cvt((a @ up(b) + t @ lb^T) * scale) + bias).  t and lb_prepacked come from comfy_feather/lora.py:fused_lora_operands."""
+    final_dtype = out_dtype if final_dtype is None else final_dtype
+    if final_dtype not in (torch.float16, torch.bfloat16) or out_dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("out_dtype and final_dtype must be float16 or bfloat16")
+    out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=final_dtype)
+    _validate(a, b_prepacked, scale, bias, out, 1, allow_bf16_a=True, bias_dtype=out_dtype)
+    if a.shape[0] != 0:
+        native.scaled_mm_lora_into(a, b_prepacked, scale, bias, out, t, lb_prepacked, out_dtype=out_dtype)
+    return out
+
+
 def prepack_b_for_scaled_mm(b: torch.Tensor) -> torch.Tensor:
     """(K, N) -> (K/16, N, 16): out[kb, n, j] = b[16*kb + j, n]."""
     if b.dim() != 2 or b.shape[0] % 16 != 0:

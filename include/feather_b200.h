@@ -123,6 +123,23 @@ FEATHER_API int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_
                                         const feather_mm_variant* variant, void* workspace, size_t workspace_bytes, int* status_dev,
                                         feather_stream_t stream);
 
+/* The linear with an un-merged (low-VRAM) LoRA term folded into the GEMM's accumulator instead of added to the output afterwards
+ * (comfy_feather/lora.py:4-35 of the reference computes y += ((x A^T) B^T) * strength with two GEMMs and a read-modify-write of
+ * the whole [M, N] output per patch):
+ *     c = cast( cvt( (a . up(W) + t . lb^T) * scale ) + bias )
+ * after the weight's k-blocks every tile runs rank/64 more blocks whose operands are already 16-bit:
+ *   t             [M, rank]  row-major, dtype of `a`: the down-projection x A^T of all patches side by side, times a power of two alpha
+ *   lb_prepacked  [rank/8, N, 8], dtype of `a`: lb[j][n][i] = B'[n][8j + i] with B' = B * strength / (scale * alpha), so that
+ *                 (t . lb^T) * scale is the LoRA term (alpha only moves both factors into the 16-bit range)
+ *   rank          total rank of all patches, padded with zero columns to a multiple of 64
+ * Everything else as feather_scaled_mm_typed with e5m2 weights; the variant must not split K.  The tensor-memory kernel is used
+ * for any M.  The result differs from the reference's sequence by its roundings only (one rounding of the sum instead of one per
+ * patch). */
+FEATHER_API int feather_scaled_mm_lora(const void* a, int a_dtype, const uint8_t* b_prepacked, const float* scale, const void* bias, void* c,
+                                       int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, int final_dtype, const void* t,
+                                       const void* lb_prepacked, int64_t rank, const feather_mm_variant* variant, int* status_dev,
+                                       feather_stream_t stream);
+
 /* Column-sharded linear over the GPUs of one box, exchange fused into the GEMM: the same launch as feather_scaled_mm_ex,
  * but every finished output block is stored (TMA store) to each of the n_dst buffers in c_list_host - a HOST array of device
  * pointers: entry 0 the caller's own [M, ldc] buffer (already offset to this rank's first column), the others the same position

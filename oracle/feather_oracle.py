@@ -241,6 +241,28 @@ def scaled_mm(a, b_prepacked, scale, bias, out_dtype, product="fp32", b_format="
     return from_f32(out, out_dtype)
 
 
+def scaled_mm_lora(a, b_prepacked, scale, bias, out_dtype, terms, a_format="fp16", final_dtype=None):
+    """The linear with un-merged LoRA terms added before the rounding: cvt((a @ up(b)) * scale + sum_p (a A_p^T) B_p^T s_p) + bias.
+    `terms` is a list of (lora_a [r,K], lora_b [N,r], strength) as float arrays.  This is what folding the patches of
+    comfy_feather/lora.py:4-35 into the GEMM computes; the reference adds each patch to the rounded output instead, so the two
+    differ by roundings only.  Evaluated in float64, rounded once."""
+    kb, n, _ = b_prepacked.shape
+    w = e5m2_bits_to_f32(b_prepacked.transpose(0, 2, 1).reshape(kb * 16, n)).astype(np.float64)
+    a64 = np.asarray(a, dtype=np.float16).astype(np.float64) if a_format == "fp16" else bf16_bits_to_f32(a).astype(np.float64)
+    acc = a64 @ w
+    if scale is not None:
+        acc = acc * float(scale)
+    for lora_a, lora_b, strength in terms:
+        acc = acc + ((a64 @ np.asarray(lora_a, dtype=np.float64).T) @ np.asarray(lora_b, dtype=np.float64).T) * float(strength)
+    with np.errstate(invalid="ignore", over="ignore"):
+        out = round_to(acc.astype(np.float32), out_dtype)
+        if bias is not None:
+            out = round_to(out + to_f32(bias, out_dtype)[None, :], out_dtype)
+        if final_dtype is not None and final_dtype != out_dtype:
+            return from_f32(round_to(out, final_dtype), final_dtype)
+    return from_f32(out, out_dtype)
+
+
 def lora_delta(x_f32, lora_a, lora_b, lora_scale):
     """(x A^T) B^T * s in float64: the un-merged LoRA term of comfy_feather/lora.py:30-33 (checker for its tests)."""
     t = np.asarray(x_f32, dtype=np.float64) @ np.asarray(lora_a, dtype=np.float64).T
