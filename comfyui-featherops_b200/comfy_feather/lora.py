@@ -50,7 +50,8 @@ def fused_lora_operands(x, weight_functions, weight_scale):
 
     x [M, K] fp16 / bf16 on the GPU (the activations the GEMM will see); weight_scale: fp32 one-element tensor, the scale of
     the quantised weight.  The GEMM computes (x W + t lb^T) * scale, so lb carries strength / scale; a power of two alpha
-    moves t up and lb down so that both fit the 16-bit dtype (for fp16: |t| <= 16384):
+    moves t up and lb down so that both fit fp16 (|t| <= 16384), which both are whatever x's dtype - the kernel runs the
+    low-rank blocks as fp16 x fp16 MMAs, so the term keeps 11 significant bits per operand also in a bf16 model:
         t  = (x A^T) * alpha                                [M, R]    A = all patches' lora_A stacked, R padded to a multiple of 64
         lb = B * strength / (scale * alpha), prepacked      [R/8, N, 8]
     Everything stays on the device (no synchronisation)."""
@@ -67,11 +68,14 @@ def fused_lora_operands(x, weight_functions, weight_scale):
     if pad:
         a_cat = F.pad(a_cat, (0, 0, 0, pad))
         b_cat = F.pad(b_cat, (0, pad))
-    down = F.linear(x, a_cat).float()                                                                            # [M, R]: a plain library GEMM
+    try:                                                                                                         # [M, R]: a plain library GEMM,
+        down = torch.mm(x, a_cat.t(), out_dtype=torch.float32)                                                   # kept in fp32 where torch can
+    except (TypeError, RuntimeError):
+        down = F.linear(x, a_cat).float()
     amax = down.abs().amax().clamp_min(1e-30)
     alpha = torch.exp2(torch.floor(torch.log2(16384.0 / amax))).clamp(2.0 ** -24, 2.0 ** 24)                      # power of two: the scaling of t is exact
-    t = (down * alpha).to(dt).contiguous()
-    lb = (b_cat / (weight_scale.to(device=dev, dtype=torch.float32).reshape(()) * alpha)).to(dt)                  # [N, R], one rounding
+    t = (down * alpha).to(torch.float16).contiguous()
+    lb = (b_cat / (weight_scale.to(device=dev, dtype=torch.float32).reshape(()) * alpha)).to(torch.float16)       # [N, R], one rounding
     n, r = lb.shape
     lb_prepacked = lb.view(n, r // 8, 8).permute(1, 0, 2).contiguous()                                           # [R/8, N, 8]
     return t, lb_prepacked

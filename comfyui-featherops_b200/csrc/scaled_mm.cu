@@ -127,7 +127,8 @@ struct MmParams {
     float scale_mul;
     // Un-merged LoRA folded into the accumulator: after the weight's k-blocks every tile runs lora_blocks more blocks of 64
     // "k" each, whose token operand is T' [M, R] (the down-projected activations) and whose weight operand is B' [R/8, N, 8],
-    // both already in the 16-bit format of the MMA (no upcast), scaled so that T' B'^T = (x A^T) B^T * strength / scale.
+    // both fp16 whatever the activations' dtype (the format is a field of each MMA instruction; no upcast), scaled so that
+    // T' B'^T = (x A^T) B^T * strength / scale.
     int lora_blocks;
     int a3d;       // 1: the token tensor map is the 3-D form (64 k, M, K/64): one copy per k-block
     int c3d;       // 1: the output tensor maps are the 3-D form (64 n, M, N/64): one store per staged block and destination
@@ -457,7 +458,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (warp == kMmaWarp || (kIssuers == 2 && warp == kMma2Warp)) {
         // ------------------------------------------------------------------ MMA issuers (leader CTA, one lane per issuing warp)
         if (rank == 0 && lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(kBW * CG, TN, p.a_bf16 != 0);
+            const uint32_t idesc_main = umma_idesc_f16(kBW * CG, TN, p.a_bf16 != 0);
+            constexpr uint32_t idesc_low_rank = umma_idesc_f16(kBW * CG, TN, false);   // the LoRA term's operands are always fp16
             const uint32_t issuer = warp == kMmaWarp ? 0u : 1u;
             // One lane runs this loop (a loop that the whole warp runs in lockstep, with lane 0 issuing, measured slower: its
             // waits cost more).  It is written for instruction count: for tiles narrower than 256 tokens the tensor pipe
@@ -520,6 +522,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint32_t a_tmem = tmem_wring + s * kTColsPerStage;
                     const uint64_t b_stage = desc0 + static_cast<uint64_t>(s * (C::kAStageBytes >> 4));
                     const int sub_tiles = i >= w.kb_count ? 1 : kSubTiles;              // a low-rank block holds 64 k: one sub-tile
+                    const uint32_t idesc = i >= w.kb_count ? idesc_low_rank : idesc_main;
 #pragma unroll
                     for (int sub = 0; sub < kSubTiles; ++sub) {
                         if (sub < sub_tiles) {
@@ -620,7 +623,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                      : "=r"(x[j][0]), "=r"(x[j][1]), "=r"(x[j][2]), "=r"(x[j][3])
                                      : "r"(src + j * (kBW * 16)));
                     if (low_rank) {
-                        // B' is already in the MMA's 16-bit format: 16 bytes are 8 ranks = 4 tensor-memory columns, no upcast
+                        // B' is fp16 already: 16 bytes are 8 ranks = 4 tensor-memory columns, no upcast
 #pragma unroll
                         for (int j = 0; j < kKSteps; ++j) tmem_st_32x32b_x4(dst + j * 4, x[j]);
                     } else if (up_mode == 0) {
@@ -1241,7 +1244,7 @@ struct Types {
     bool a_bf16 = false;     // activations are bf16
     bool w_e4m3 = false;     // weights are fp8e4m3fn
     int final_dtype = -1;    // dtype stored (FEATHER_OUT_*); -1: the output dtype itself
-    // un-merged LoRA term folded into the accumulator (null: none): t = T' [M, R], lb = B' [R/8, N, 8], both in the activations' dtype
+    // un-merged LoRA term folded into the accumulator (null: none): t = T' [M, R], lb = B' [R/8, N, 8], both fp16
     const void* lora_t = nullptr;
     const void* lora_b = nullptr;
     int64_t lora_rank = 0;

@@ -396,14 +396,14 @@ def scaled_mm_typed_into(a, b_prepacked, scale, bias, c, out_dtype=None, variant
 
 def scaled_mm_lora_into(a, b_prepacked, scale, bias, c, t, lb_prepacked, out_dtype=None, variant=None):
     """c = cast(cvt((a @ up(b) + t @ lb^T) * scale) + bias): the linear with an un-merged LoRA term folded into the accumulator.
-    t [M, R] and lb_prepacked [R/8, N, 8] have a's dtype (fp16 or bf16), R a multiple of 64; see `feather_scaled_mm_lora`."""
+    t [M, R] and lb_prepacked [R/8, N, 8] are fp16 (whatever a's dtype), R a multiple of 64; see `feather_scaled_mm_lora`."""
     lib = load_library()
     dev = _require_cuda(a, b_prepacked, scale, bias, c, t, lb_prepacked)
     M, K = a.shape
     N = b_prepacked.shape[1]
     R = t.shape[1]
-    if t.shape != (M, R) or lb_prepacked.shape != (R // 8, N, 8) or t.dtype != a.dtype or lb_prepacked.dtype != a.dtype:
-        raise FeatherNativeError("LoRA term: t must be [M, R] and lb_prepacked [R/8, N, 8], both in the activations' dtype")
+    if t.shape != (M, R) or lb_prepacked.shape != (R // 8, N, 8) or t.dtype != torch.float16 or lb_prepacked.dtype != torch.float16:
+        raise FeatherNativeError("LoRA term: t must be [M, R] and lb_prepacked [R/8, N, 8], both float16")
     if not (t.is_contiguous() and lb_prepacked.is_contiguous()):
         raise FeatherNativeError("LoRA term: t and lb_prepacked must be contiguous")
     out_dtype = c.dtype if out_dtype is None else out_dtype

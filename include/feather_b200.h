@@ -128,9 +128,10 @@ FEATHER_API int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_
  * the whole [M, N] output per patch):
  *     c = cast( cvt( (a . up(W) + t . lb^T) * scale ) + bias )
  * after the weight's k-blocks every tile runs rank/64 more blocks whose operands are already 16-bit:
- *   t             [M, rank]  row-major, dtype of `a`: the down-projection x A^T of all patches side by side, times a power of two alpha
- *   lb_prepacked  [rank/8, N, 8], dtype of `a`: lb[j][n][i] = B'[n][8j + i] with B' = B * strength / (scale * alpha), so that
- *                 (t . lb^T) * scale is the LoRA term (alpha only moves both factors into the 16-bit range)
+ *   t             [M, rank]  row-major, fp16 (also with bf16 activations: the low-rank blocks run as fp16 x fp16 MMAs into the same
+ *                 accumulator): the down-projection x A^T of all patches side by side, times a power of two alpha
+ *   lb_prepacked  [rank/8, N, 8] fp16: lb[j][n][i] = B'[n][8j + i] with B' = B * strength / (scale * alpha), so that
+ *                 (t . lb^T) * scale is the LoRA term (alpha only moves both factors into fp16's range)
  *   rank          total rank of all patches, padded with zero columns to a multiple of 64
  * Everything else as feather_scaled_mm_typed with e5m2 weights; the variant must not split K.  The tensor-memory kernel is used
  * for any M.  The result differs from the reference's sequence by its roundings only (one rounding of the sum instead of one per

@@ -64,8 +64,8 @@ def test_fused_lora_against_the_oracle(pkg, native, hip_kernel, cuda_dev, dtype,
     native.check_device_status(cuda_dev)
     a_np = from_torch(x)
     ref = fo.scaled_mm_lora(a_np, bq, s, bias, dtype, terms, a_format=dtype)
-    # the term's operands are rounded to 16 bits (t and lb), so its error scales with the dtype's precision
-    _gate(from_torch(y), ref, dtype, f"{(M, N, K, ranks)} {dtype}", fro_limit=2e-3 if dtype == "fp16" else 6e-3)
+    # the term's operands t and lb are fp16 also in a bf16 model (the down-projection is kept in fp32 until it is scaled)
+    _gate(from_torch(y), ref, dtype, f"{(M, N, K, ranks)} {dtype}", fro_limit=2e-3 if dtype == "fp16" else 4e-3)
     # the linear alone must be untouched by the extra blocks: zero LoRA matrices give the plain result bit for bit
     zero = [_PatchFn([(1.0, _Adapter(torch.zeros(N, 8), torch.zeros(8, K), None), 1.0, None, None)])]
     t0, lb0 = lora.fused_lora_operands(X, zero, S)
