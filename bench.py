@@ -112,7 +112,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wan", choices=["wan", "qwen", "smallm", "quant", "dit"])
+    ap.add_argument("--workload", default="wan", choices=["wan", "qwen", "smallm", "quant", "dit", "lora"])
     ap.add_argument("--dit-mode", default="all_gather", choices=["all_gather", "pairs"])
     ap.add_argument("--tokens", type=int, default=32768, help="dit: token count")
     ap.add_argument("--blocks", type=int, default=4, help="dit: transformer blocks")
@@ -277,6 +277,8 @@ def run_ours(args):
         return run_quant(args, native, dev)
     if args.workload == "dit" and not args.shape:
         return run_dit(args, native, dev, world, rank, local)
+    if args.workload == "lora" and not args.shape:
+        return run_lora(args, native, hk, dev)
 
     M, kn_list, out_dtype, desc = shapes_for(args)
     odt = TORCH_DT[out_dtype]
@@ -734,6 +736,60 @@ def run_dit(args, native, dev, world, rank, local):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_lora(args, native, hk, dev):
+    """Un-merged LoRA on the Wan ffn-up linear (M = 32768, K = 5120, N = 13824, bf16 model, rank 64): the patch folded into the
+    GEMM's accumulator (`scaled_mm_lora`) against the reference's sequence (linear, two GEMMs, y += up * strength)."""
+    # loaded by path: importing the comfy_feather package would pull in the ComfyUI loader node
+    spec = importlib.util.spec_from_file_location("feather_b200_lora", os.path.join(ROOT, "comfyui-featherops_b200", "comfy_feather", "lora.py"))
+    lora = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(lora)
+    M, K, N, r = 32768, 5120, 13824, 64
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+    w = torch.randn((N, K), generator=g, device=dev) / K ** 0.5
+    bq, s = native.quantize_prepack(w)
+    s = s.reshape(1)
+    del w
+    A = torch.randn((r, K), generator=g, device=dev) / K ** 0.5
+    B = torch.randn((N, r), generator=g, device=dev) / r ** 0.5
+
+    class Adapter:
+        weights = (B, A, float(r), None, None, None)
+
+    class PatchFn:
+        key = "w"
+        patches = {"w": [(1.0, Adapter(), 1.0, None, None)]}
+
+    patch = [PatchFn()]
+
+    def plain():
+        return hk.scaled_mm_b200(x, bq, s, None, torch.bfloat16, torch.bfloat16)
+
+    def unfused():
+        return lora.apply_lora_patches(x, plain(), patch)
+
+    def fused():
+        t, lb = lora.fused_lora_operands(x, patch, s)
+        return hk.scaled_mm_lora(x, bq, s, None, torch.bfloat16, torch.bfloat16, t, lb)
+
+    rows = {}
+    for name, fn in (("linear alone", plain), ("reference sequence (linear, 2 GEMMs, add)", unfused), ("folded into the GEMM (operands prepared every call)", fused)):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        rows[name] = round(e0.elapsed_time(e1) / args.steps, 4)
+    diff = (fused().float() - unfused().float()).abs().max().item()
+    native.check_device_status(dev)
+    print(json.dumps({"metric": "ms per call, Wan ffn-up linear with one un-merged rank-64 LoRA patch, bf16 model", "unit": "ms", "M": M, "K": K, "N": N, "rank": r,
+                      "ms": rows, "max_abs_difference_between_the_two": diff}), flush=True)
 
 
 def run_quant(args, native, dev):

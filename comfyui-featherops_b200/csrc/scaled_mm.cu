@@ -262,7 +262,10 @@ __device__ __forceinline__ uint32_t finish_pair(float acc0, float acc1, float sc
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int TN, int CG, int TG, int OB = 1>
+// EXT = false is the plain linear (fp16 activations, e5m2 weights, every block stored to all destinations); EXT = true adds, as
+// run-time switches, bf16 activations, e4m3 weights, the low-rank (LoRA) blocks and row-sharded destinations.  The split keeps
+// the single-thread loops of the plain kernel free of those branches: with them in, the Wan shapes ran 2-4 % slower.
+template <int TN, int CG, int TG, int OB = 1, bool EXT = false>
 __global__ void __launch_bounds__(32 * (kEpilogueWarps + 4 * TG + 2 + Cfg<TN, CG>::kIssuers), 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ OutMaps tmap_c, const __grid_constant__ LoraMaps tmap_l, const MmParams p) {
@@ -374,9 +377,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
                     const Unit w = decode_unit<TN, CG>(p, u);
                     int kb = w.kb_begin;
-                    for (int i = 0; i < w.kb_total; ++i, ++kb, ++it) {
-                        const bool low_rank = i >= w.kb_count;                       // block e = i - kb_count of the LoRA term
-                        const int e = i - w.kb_count;
+                    const int kb_total = EXT ? w.kb_total : w.kb_count;
+                    for (int i = 0; i < kb_total; ++i, ++kb, ++it) {
+                        const bool low_rank = EXT && i >= w.kb_count;                // block e = i - kb_count of the LoRA term
+                        [[maybe_unused]] const int e = i - w.kb_count;
                         tw.start();
                         const bool free_ok = mbar_wait_warp(bar_free + 8 * s, ph ^ 1u, abort_flag, lane);
                         tw.stop(st_wait);
@@ -458,8 +462,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (warp == kMmaWarp || (kIssuers == 2 && warp == kMma2Warp)) {
         // ------------------------------------------------------------------ MMA issuers (leader CTA, one lane per issuing warp)
         if (rank == 0 && lane == 0) {
-            const uint32_t idesc_main = umma_idesc_f16(kBW * CG, TN, p.a_bf16 != 0);
-            constexpr uint32_t idesc_low_rank = umma_idesc_f16(kBW * CG, TN, false);   // the LoRA term's operands are always fp16
+            const uint32_t idesc_main = umma_idesc_f16(kBW * CG, TN, EXT && p.a_bf16 != 0);
+            [[maybe_unused]] constexpr uint32_t idesc_low_rank = umma_idesc_f16(kBW * CG, TN, false);   // the LoRA term's operands are always fp16
             const uint32_t issuer = warp == kMmaWarp ? 0u : 1u;
             // One lane runs this loop (a loop that the whole warp runs in lockstep, with lane 0 issuing, measured slower: its
             // waits cost more).  It is written for instruction count: for tiles narrower than 256 tokens the tensor pipe
@@ -495,7 +499,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (a * kIssuers + issuer) * TN;
                 uint32_t accumulate = 0;                                          // this issuer's first MMA of a tile overwrites its accumulator
-                for (int i = 0; i < w.kb_total; ++i) {
+                const int kb_total = EXT ? w.kb_total : w.kb_count;
+                for (int i = 0; i < kb_total; ++i) {
                     if (kIssuers == 2 && (static_cast<uint32_t>(i) & 1u) != issuer) {
                         advance(s, ph);
                         continue;
@@ -517,15 +522,16 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     uint32_t sn = s, phn = ph;
 #pragma unroll
                     for (int j = 0; j < kIssuers; ++j) advance(sn, phn);
-                    peeked = (i + kIssuers < w.kb_total) && mbar_test_wait(bar_full + 8 * sn, phn);
+                    peeked = (i + kIssuers < kb_total) && mbar_test_wait(bar_full + 8 * sn, phn);
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_wring + s * kTColsPerStage;
                     const uint64_t b_stage = desc0 + static_cast<uint64_t>(s * (C::kAStageBytes >> 4));
-                    const int sub_tiles = i >= w.kb_count ? 1 : kSubTiles;              // a low-rank block holds 64 k: one sub-tile
-                    const uint32_t idesc = i >= w.kb_count ? idesc_low_rank : idesc_main;
+                    const bool low_rank = EXT && i >= w.kb_count;
+                    const int sub_tiles = low_rank ? 1 : kSubTiles;                    // a low-rank block holds 64 k: one sub-tile
+                    const uint32_t idesc = low_rank ? idesc_low_rank : idesc_main;
 #pragma unroll
                     for (int sub = 0; sub < kSubTiles; ++sub) {
-                        if (sub < sub_tiles) {
+                        if (!EXT || sub < sub_tiles) {
 #pragma unroll
                             for (int ks = 0; ks < kSubK / 16; ++ks) {
                                 // +32 bytes of K inside the 128-byte swizzle row = +2 in the descriptor's address field
@@ -576,7 +582,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int g = (warp - kFirstTransformWarp) >> 2;
         const uint32_t w_lane_off = static_cast<uint32_t>(q * 32 + lane) * 16u;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
-        const int up_mode = (p.a_bf16 ? 1 : 0) | (p.w_e4m3 ? 2 : 0);
+        const int up_mode = EXT ? ((p.a_bf16 ? 1 : 0) | (p.w_e4m3 ? 2 : 0)) : 0;
         // Running ring positions of the next k-block (weight-byte ring, operand ring) and whose turn it is; no division in the loop.
         uint32_t ws = 0, wph = 0, os = 0, oph = 0;
         int turn = 0;
@@ -587,9 +593,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tt.start();
         for (int u = cluster_id; ok && u < p.num_units; u += num_clusters) {
             const Unit w = decode_unit<TN, CG>(p, u);
-            for (int i = 0; i < w.kb_total; ++i) {
+            const int kb_total = EXT ? w.kb_total : w.kb_count;
+            for (int i = 0; i < kb_total; ++i) {
                 const uint32_t s = ws, ph = wph, t = os, tph = oph;
-                const bool low_rank = i >= w.kb_count;
+                const bool low_rank = EXT && i >= w.kb_count;
                 const bool mine = turn == g;
                 if (++ws == kWStages) {
                     ws = 0;
@@ -678,7 +685,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const int grp = warp >> 2;
         const bool group_leader = (threadIdx.x & 127) == 0;
         const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
-        const float scale = (p.scale != nullptr ? __ldg(p.scale) : 1.0f) * p.scale_mul;
+        const float scale = (p.scale != nullptr ? __ldg(p.scale) : 1.0f) * (EXT ? p.scale_mul : 1.0f);
         const bool out_bf16 = p.out_bf16 != 0;
         const bool flip = p.flip_final != 0;
         const bool has_bias = p.bias != nullptr;
@@ -718,7 +725,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t src = tmem_base + t_lane + a * (kIssuers * TN);
             // With two issuers the tile's sum is split over two accumulators (even / odd k-blocks); a tile of one k-block has
             // nothing in the second.
-            const bool two_sums = kIssuers == 2 && w.kb_total >= 2;
+            const bool two_sums = kIssuers == 2 && (EXT ? w.kb_total : w.kb_count) >= 2;
             // 16 accumulator columns starting at column c0 -> registers (fp32 bit patterns), both partial sums added.
             auto load_sum16 = [&](int c0, uint32_t (&v)[16]) {
                 tmem_ld_32x32b_x16(src + c0, v);
@@ -831,7 +838,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         if (group_leader) {
                             // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
                             int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
-                            if (p.scatter_rows > 0 && d_end > 0) {
+                            if (EXT && p.scatter_rows > 0 && d_end > 0) {
                                 // row-sharded destinations: the block goes to the one buffer that owns its token rows
                                 d_begin = row / p.scatter_rows;
                                 row -= d_begin * p.scatter_rows;
@@ -1188,11 +1195,11 @@ static bool make_plan(int64_t M, int64_t N, int64_t K, const feather_mm_variant*
     return true;
 }
 
-template <int TN, int CG, int TG, int OB = 1>
+template <int TN, int CG, int TG, int OB = 1, bool EXT = false>
 static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl, const MmParams& p, int grid,
                                   cudaStream_t stream) {
     using C = Cfg<TN, CG, OB>;
-    auto kernel = scaled_mm_kernel<TN, CG, TG, OB>;
+    auto kernel = scaled_mm_kernel<TN, CG, TG, OB, EXT>;
     static std::mutex mu;
     static bool configured[64];
     int dev = 0;
@@ -1224,15 +1231,15 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
     return cudaLaunchKernelEx(&cfg, kernel, tw, ta, tc, tl, p);
 }
 
-template <int TN>
+template <int TN, bool EXT>
 static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl,
                              const MmParams& p, int grid, cudaStream_t s) {
-    if constexpr (TN == 256) {
+    if constexpr (TN == 256 && !EXT) {
         // pairs of 256-token tiles whose blocks also cross NVLink: two staging buffers per epilogue group
         if (deep_staging && cg == 2) return tg == 1 ? launch_variant<TN, 2, 1, 2>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2, 2>(tw, ta, tc, tl, p, grid, s);
     }
-    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 1, 2>(tw, ta, tc, tl, p, grid, s);
-    return tg == 1 ? launch_variant<TN, 2, 1>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2>(tw, ta, tc, tl, p, grid, s);
+    if (cg == 1) return tg == 1 ? launch_variant<TN, 1, 1, 1, EXT>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 1, 2, 1, EXT>(tw, ta, tc, tl, p, grid, s);
+    return tg == 1 ? launch_variant<TN, 2, 1, 1, EXT>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2, 1, EXT>(tw, ta, tc, tl, p, grid, s);
 }
 
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
@@ -1321,7 +1328,11 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
             return set_error(FEATHER_ERR_WORKSPACE, "split-K variant needs a larger workspace");
         if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return set_error(FEATHER_ERR_BAD_ARGUMENT, "workspace must be 16-byte aligned");
     }
-    const int tg = pl.tg;
+    // Upcasting to bf16 or from e4m3 takes several instructions per pair where e5m2 -> fp16 takes one `prmt`: with a single
+    // transform group the upcast then sets the pace of 256-token tiles (measured 4.7-6.0 ms against 3.6 ms with two groups on the
+    // Wan ffn-up shape), so those operand types get two groups unless the caller pinned the number.
+    const bool slow_upcast = types.a_bf16 || types.w_e4m3;
+    const int tg = (slow_upcast && !(variant && variant->transform_groups != 0)) ? 2 : pl.tg;
 
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) return set_error(FEATHER_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
@@ -1435,14 +1446,16 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
     if (clusters > pl.num_units) clusters = pl.num_units;
     const int grid = clusters * pl.cg;
 
+    // the plain kernel, or the one with the run-time switches for operand types, low-rank blocks and row-sharded destinations
+    const bool ext = types.a_bf16 || types.w_e4m3 || lora || scatter_rows > 0;
     cudaError_t e = cudaErrorInvalidValue;
     switch (pl.tn) {
-        case 16: e = launch_tn<16>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
-        case 32: e = launch_tn<32>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
-        case 64: e = launch_tn<64>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
-        case 128: e = launch_tn<128>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
-        case 192: e = launch_tn<192>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
-        case 256: e = launch_tn<256>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 16: e = ext ? launch_tn<16, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<16, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 32: e = ext ? launch_tn<32, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<32, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 64: e = ext ? launch_tn<64, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<64, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 128: e = ext ? launch_tn<128, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<128, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 192: e = ext ? launch_tn<192, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<192, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
+        case 256: e = ext ? launch_tn<256, true>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream) : launch_tn<256, false>(pl.cg, tg, deep_staging, tmap_w, tmap_a, tmap_c, tmap_l, p, grid, stream); break;
         default: break;
     }
     if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "scaled_mm launch failed: %s", cudaGetErrorString(e));
