@@ -117,6 +117,7 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=32768, help="dit: token count")
     ap.add_argument("--blocks", type=int, default=4, help="dit: transformer blocks")
     ap.add_argument("--no-small-m", action="store_true", help="skip the small_m sub-record of the default N = 1 line")
+    ap.add_argument("--a-dtype", default="fp16", choices=["fp16", "bf16"], help="one GPU: activation dtype (bf16 goes through feather_scaled_mm_typed)")
     ap.add_argument("--shape", default=None, help="M,N,K: time a single GEMM instead of a workload")
     ap.add_argument("--variant", default=None, help="tokens_tile,cta_pair,split_k,transform_groups,max_ctas (0 = auto)")
     ap.add_argument("--out-dtype", default=None, choices=["bf16", "fp16"])
@@ -295,12 +296,22 @@ def run_ours(args):
         layers.append((a, lin, K, N, bq if world > 1 else None))
     torch.cuda.synchronize()
 
+    typed_outputs = None
+    if args.a_dtype == "bf16":
+        if world != 1:
+            raise SystemExit("--a-dtype bf16 is a one-GPU option")
+        layers = [(a.to(torch.bfloat16), lin, K, N, x) for a, lin, K, N, x in layers]
+        typed_outputs = [torch.empty((M, N), dtype=odt, device=dev) for _, _, _, N, _ in layers]
+
     def step(events=None):
-        for a, lin, K, N, _ in layers:
+        for li, (a, lin, K, N, _) in enumerate(layers):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            lin(a, odt, variant=variant)
+            if typed_outputs is not None:
+                native.scaled_mm_typed_into(a, lin.b_local, lin.scale, None, typed_outputs[li], variant=variant)
+            else:
+                lin(a, odt, variant=variant)
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
@@ -375,7 +386,10 @@ def run_ours(args):
         torch.cuda.synchronize()
         k0.record()
         for _ in range(reps):
-            lin.gemm_only(a, odt, variant=variant)
+            if typed_outputs is not None:
+                native.scaled_mm_typed_into(a, lin.b_local, lin.scale, None, typed_outputs[li], variant=variant)
+            else:
+                lin.gemm_only(a, odt, variant=variant)
         k1.record()
         torch.cuda.synchronize()
         t_ms = k0.elapsed_time(k1) / reps
@@ -423,7 +437,7 @@ def run_ours(args):
     # end to end through the operator with host buffers: pinned H2D of the activations, D2H of the output, every step
     e2e = None
     if not args.no_e2e:
-        e2e = run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps=max(2, min(args.steps, 5)), variant=variant)
+        e2e = run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps=max(2, min(args.steps, 5)), variant=variant) if typed_outputs is None else None
 
     small_m = None
     if world == 1 and args.workload == "wan" and not args.shape and not args.no_small_m:

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC_DIR = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libfeather_b200.so")
-SOURCES = ["scaled_mm.cu", "quant.cu", "small_m.cu", "exchange.cu"]
+SOURCES = ["scaled_mm.cu", "scaled_mm_ext.cu", "quant.cu", "small_m.cu", "exchange.cu"]
 HEADERS = ["ptx.cuh", "host_util.h", os.path.join("..", "..", "include", "feather_b200.h")]
 
 NVCC_FLAGS = [

@@ -1232,7 +1232,7 @@ static cudaError_t launch_variant(const CUtensorMap& tw, const CUtensorMap& ta, 
 }
 
 template <int TN, bool EXT>
-static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl,
+cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMap& tw, const CUtensorMap& ta, const OutMaps& tc, const LoraMaps& tl,
                              const MmParams& p, int grid, cudaStream_t s) {
     if constexpr (TN == 256 && !EXT) {
         // pairs of 256-token tiles whose blocks also cross NVLink: two staging buffers per epilogue group
@@ -1242,6 +1242,20 @@ static cudaError_t launch_tn(int cg, int tg, bool deep_staging, const CUtensorMa
     return tg == 1 ? launch_variant<TN, 2, 1, 1, EXT>(tw, ta, tc, tl, p, grid, s) : launch_variant<TN, 2, 2, 1, EXT>(tw, ta, tc, tl, p, grid, s);
 }
 
+// The extended instantiations (EXT = true) are compiled in a translation unit of their own (scaled_mm_ext.cu includes this
+// file with FEATHER_TU_EXT defined and stops after the explicit instantiations below), so the two halves build in parallel.
+#define FEATHER_FOR_EACH_TN(X) X(16) X(32) X(64) X(128) X(192) X(256)
+#ifdef FEATHER_TU_EXT
+#define FEATHER_INSTANTIATE(TN_) \
+    template cudaError_t launch_tn<TN_, true>(int, int, bool, const CUtensorMap&, const CUtensorMap&, const OutMaps&, const LoraMaps&, const MmParams&, int, cudaStream_t);
+FEATHER_FOR_EACH_TN(FEATHER_INSTANTIATE)
+#else
+#define FEATHER_DECLARE(TN_) \
+    extern template cudaError_t launch_tn<TN_, true>(int, int, bool, const CUtensorMap&, const CUtensorMap&, const OutMaps&, const LoraMaps&, const MmParams&, int, cudaStream_t);
+FEATHER_FOR_EACH_TN(FEATHER_DECLARE)
+#endif
+
+#ifndef FEATHER_TU_EXT
 int small_m_launch(const void* a, const uint8_t* w, const float* scale, const void* bias, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                    int output_dtype, int flip_final, int sms, void* workspace, size_t workspace_bytes, cudaStream_t stream);   // small_m.cu
 size_t small_m_workspace_bytes(int64_t M, int64_t N, int64_t K, int sms);                                                    // small_m.cu
@@ -1637,3 +1651,6 @@ extern "C" int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t 
     out->staging = 0;
     return FEATHER_OK;
 }
+#else
+}  // namespace feather
+#endif  // FEATHER_TU_EXT
