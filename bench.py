@@ -6,8 +6,11 @@
 
 A step is one pass over the workload's linears (default: the three Wan-2.1-14B shapes at M = 32768 tokens, bf16 out).
 One JSON line is printed by rank 0.  For N > 1 (launched with torch.distributed.run) every GEMM is sharded by weight
-columns across the ranks and its output exchanged: by default the GEMM's own epilogue TMA-stores every finished block into
-all ranks' output buffers over NVLink (`--exchange peer_store`); `--exchange all_gather` is the NCCL all-gather baseline.
+columns across the ranks and its output exchanged.  `--exchange copy_engine` (default for this workload, whose linears are
+independent): the GEMM writes its column block and copy engines push it to the peers on a second stream under the next
+linear's GEMM.  `--exchange peer_store` (default for the DiT, where the next operation needs the output at once): the GEMM's
+own epilogue TMA-stores every finished block into all ranks' output buffers over NVLink.  The line reports the step with the
+other of the two as `exchange.alternative`.  `--exchange all_gather` is the NCCL all-gather baseline.
 After the warm-up, and outside the timed region, every rank compares rows of each exchanged output bit for bit with an
 unsharded GEMM of the same rows (`exchange_check` in the line; a mismatch fails the run).
 
@@ -124,9 +127,14 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-rows", type=int, default=2048)
-    ap.add_argument("--exchange", default="peer_store", choices=["peer_store", "all_gather"],
-                    help="N > 1: fused peer-store epilogue over symmetric memory, or NCCL all-gather + relayout")
-    return ap.parse_args()
+    ap.add_argument("--exchange", default=None, choices=["copy_engine", "peer_store", "all_gather"],
+                    help="N > 1: copy engines push each finished column block to the peers on a second stream under the next linear's GEMM; "
+                         "fused peer-store epilogue over symmetric memory; or NCCL all-gather + relayout")
+    ap.add_argument("--no-alt-exchange", action="store_true", help="N > 1: do not also time the step with the other of copy_engine / peer_store")
+    args = ap.parse_args()
+    if args.exchange is None:
+        args.exchange = "peer_store" if args.workload == "dit" else "copy_engine"
+    return args
 
 
 def dist_env():
@@ -153,6 +161,9 @@ def config_for(args, M, kn_list, out_dtype, desc, world):
              else "(not larger than twice the 126 MB L2 and no flush between launches: a probe shape, not a bench line)"))
     if world == 1:
         par = "single GPU"
+    elif args.exchange == "copy_engine":
+        par = (f"weights sharded by output columns over {world} GPUs; each rank's GEMM writes its column block of the [M,N] output and copy engines "
+               "push the block to every peer over NVLink on a second stream while the next linear's GEMM runs; one cross-rank barrier per linear on that stream")
     elif args.exchange == "peer_store":
         par = (f"weights sharded by output columns over {world} GPUs; each rank's epilogue TMA-stores its blocks into every rank's output "
                "over NVLink (fused exchange), one cross-rank barrier per linear")
@@ -303,13 +314,21 @@ def run_ours(args):
         layers = [(a.to(torch.bfloat16), lin, K, N, x) for a, lin, K, N, x in layers]
         typed_outputs = [torch.empty((M, N), dtype=odt, device=dev) for _, _, _, N, _ in layers]
 
-    def step(events=None):
+    # The three linears of a step are independent, so with the copy-engine exchange nothing on the compute stream waits for a
+    # transfer: the exchange of one linear runs under the GEMM of the next (and of the next step's first).  The timed region
+    # ends only after the compute stream has waited for every exchange.
+    deferred = world > 1 and args.exchange == "copy_engine"
+
+    def step(events=None, linears=None):
         for li, (a, lin, K, N, _) in enumerate(layers):
+            lin = linears[li] if linears is not None else lin
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record()
             if typed_outputs is not None:
                 native.scaled_mm_typed_into(a, lin.b_local, lin.scale, None, typed_outputs[li], variant=variant)
+            elif world > 1 and lin.exchange == "copy_engine":
+                lin(a, odt, variant=variant, defer=True)
             else:
                 lin(a, odt, variant=variant)
             if events is not None:
@@ -361,6 +380,9 @@ def run_ours(args):
     e0.record()
     for _ in range(args.steps):
         step(launch_events if world == 1 else None)
+    if deferred:
+        for _, lin, _, _, _ in layers:
+            lin.wait_exchange()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -428,11 +450,35 @@ def run_ours(args):
     }
 
     exchange = None
-    if world > 1 and args.exchange == "peer_store":
+    if world > 1 and args.exchange in ("peer_store", "copy_engine"):
         out_bytes = sum(lin.bytes_out_per_call(M) for _, lin, _, _, _ in layers)
-        exchange = {"bytes_out_per_rank": out_bytes, "bytes_in_per_rank": out_bytes, "gbs_per_rank": out_bytes / (ms_per_step * 1e-3) / 1e9,
+        exchange = {"mode": args.exchange, "bytes_out_per_rank": out_bytes, "bytes_in_per_rank": out_bytes, "gbs_per_rank": out_bytes / (ms_per_step * 1e-3) / 1e9,
                     "nvlink_peer_copy_gbs": 770.0, "frac_of_peer_copy": out_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0,
                     "note": "each rank sends its column block of every output to each peer and receives theirs; the step cannot be shorter than bytes_in / link bandwidth"}
+        if not args.no_alt_exchange:
+            # the same step with the other exchange, timed the same way (same weights, buffers of its own)
+            other = "peer_store" if args.exchange == "copy_engine" else "copy_engine"
+            alt = [lin.with_exchange(other) for _, lin, _, _, _ in layers]
+            for _ in range(args.warmup):
+                step(linears=alt)
+            for lin in alt:
+                lin.wait_exchange()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(args.steps):
+                step(linears=alt)
+            for lin in alt:
+                lin.wait_exchange()
+            a1.record()
+            torch.cuda.synchronize()
+            dist.barrier()
+            t = torch.tensor([a0.elapsed_time(a1) / args.steps], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            exchange["alternative"] = {"mode": other, "ms_per_step": float(t.item()), "tflops": flops_step / (float(t.item()) * 1e-3) / 1e12}
+            del alt
+            native.check_device_status(dev)
 
     # end to end through the operator with host buffers: pinned H2D of the activations, D2H of the output, every step
     e2e = None

@@ -1,5 +1,6 @@
-// Exchange step of the row-parallel linear (K sharded across the GPUs of one box).
+// Exchange steps of the sharded linears (the GPUs of one box).
 //
+// Row-parallel linear (K sharded):
 // Every rank's GEMM has TMA-stored its partial of token rows [d*R, (d+1)*R) into slot `rank` of rank d's buffer
 // (feather_scaled_mm_scatter), so this GPU holds n_src partials [n_src][R][N] of the rows it owns.  The kernel here adds
 // them in fp32 in slot order (deterministic on every rank and every run), rounds once to the 16-bit output dtype, adds the
@@ -8,6 +9,10 @@
 // That last part is the all-gather of the reduced rows, so no separate collective follows.  Only stores cross NVLink.
 //
 // HBM-bound: reads n_src * R * N * 2 bytes (+ residual), writes R * N * 2 bytes per destination.
+//
+// Column-parallel linear (N sharded): feather_copy_block hands a finished [M, N/g] column block to a copy engine, which
+// writes it into the same columns of a peer's [M, N] buffer without taking an SM - on a second stream, under the GEMM of
+// the next linear.
 // The reference has no multi-GPU path, so nothing here has a counterpart there; the rounding and bias rules are those of
 // kernel/naive.py:34-40 (cast to the output dtype, then add the bias in that dtype).
 #include <cuda_bf16.h>
@@ -134,5 +139,18 @@ extern "C" int feather_reduce_partials(const void* partials, int n_src, int64_t 
             reinterpret_cast<const uint16_t*>(residual), ld_res, dst, n_dst, ld_dst);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "reduce_partials launch failed: %s", cudaGetErrorString(e));
+    return FEATHER_OK;
+}
+
+extern "C" int feather_copy_block(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t width_bytes, int64_t rows,
+                                  feather_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (dst == nullptr || src == nullptr) return set_error(FEATHER_ERR_BAD_ARGUMENT, "dst and src must not be null");
+    if (width_bytes < 0 || rows < 0 || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes)
+        return set_error(FEATHER_ERR_BAD_ARGUMENT, "width and rows must not be negative and no pitch smaller than the width");
+    if (width_bytes == 0 || rows == 0) return FEATHER_OK;
+    const cudaError_t e = cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch_bytes), src, static_cast<size_t>(src_pitch_bytes),
+                                            static_cast<size_t>(width_bytes), static_cast<size_t>(rows), cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return set_error(FEATHER_ERR_CUDA, "cudaMemcpy2DAsync failed: %s", cudaGetErrorString(e));
     return FEATHER_OK;
 }

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "feather_scaled_mm_multi",
     "feather_scaled_mm_scatter",
     "feather_reduce_partials",
+    "feather_copy_block",
     "feather_scaled_mm_static_scratch_bytes",
     "feather_quantize_prepack",
     "feather_prepack_bytes",
@@ -107,6 +108,8 @@ def load_library():
         lib.feather_scaled_mm_scatter.restype = ci
         lib.feather_reduce_partials.argtypes = [vp, ci, i64, i64, vp, vp, i64, ctypes.POINTER(vp), ci, i64, ci, vp]
         lib.feather_reduce_partials.restype = ci
+        lib.feather_copy_block.argtypes = [vp, i64, vp, i64, i64, i64, vp]
+        lib.feather_copy_block.restype = ci
         lib.feather_scaled_mm_static_scratch_bytes.argtypes = []
         lib.feather_scaled_mm_static_scratch_bytes.restype = sz
         lib.feather_quantize_prepack.argtypes = [vp, ci, vp, i64, i64, ci, vp, vp, vp, vp]
@@ -482,6 +485,20 @@ def reduce_partials_into(partials, bias, residual, outputs):
             ptrs, len(outputs), o0.stride(0), _OUT_CODE[partials.dtype], _stream_ptr(dev),
         )
     _check(status, "feather_reduce_partials")
+
+
+def copy_block_into(dst, src, stream=None):
+    """dst[:, :] = src[:, :] by a copy engine (`feather_copy_block`), asynchronous on `stream` (default: the current stream).
+    Both are 2-D views with unit column stride and the same shape and dtype, on this device or peer-mapped."""
+    lib = load_library()
+    dev = _require_cuda(src)
+    if dst.shape != src.shape or dst.dtype != src.dtype or dst.dim() != 2 or dst.stride(1) != 1 or src.stride(1) != 1:
+        raise FeatherNativeError("copy_block_into needs two 2-D views of one shape and dtype with unit column stride")
+    item = src.element_size()
+    raw = ctypes.c_void_p(stream.cuda_stream) if stream is not None else _stream_ptr(dev)
+    with torch.cuda.device(dev):
+        status = lib.feather_copy_block(dst.data_ptr(), dst.stride(0) * item, src.data_ptr(), src.stride(0) * item, src.shape[1] * item, src.shape[0], raw)
+    _check(status, "feather_copy_block")
 
 
 def scaled_mm_static_into(a, b_prepacked, scale, bias, c, variant=None):

@@ -12,6 +12,14 @@ ColumnShardedLinear   rank r keeps the weight columns [r*N/g, (r+1)*N/g) (dim 1)
                       after the launch ("all blocks have landed"): a rank reaches the barrier of call n only after its own
                       stream has run everything that read the output of call n-1, so once call n's barrier has passed, nobody
                       still reads the buffer that call n+1 overwrites.
+    "copy_engine"     the GEMM writes its block into its own [M, N] symmetric buffer and copy engines push the block into
+                      every peer's buffer on a second stream (`feather_copy_block`), followed by the cross-rank barrier on
+                      that stream.  No SM waits for NVLink, so the transfer overlaps whatever the compute stream runs next:
+                      with `defer=True` the call returns at once and the caller orders its reads with `wait_exchange()`
+                      (independent linears in a row: the exchange of one runs under the GEMM of the next); without it
+                      the compute stream waits for the exchange before it goes on.  From 4 GPUs on, where the exchange of
+                      these shapes takes longer than the GEMM, this is the faster form when there is independent work to
+                      overlap; the fused form is faster when the next operation needs the output at once.
     "all_gather"      `all_gather_into_tensor` (NCCL) of the [M, N/g] blocks, then a relayout copy to [M, N].  Baseline.
     "none"            no exchange: the call returns the local [M, N/g] block (first half of a tensor-parallel pair).
 
@@ -74,13 +82,27 @@ class _SymmetricBuffers:
         return entry
 
 
+_exchange_streams = {}
+
+
+def exchange_stream(device):
+    """The second stream of `device` that carries the copy-engine exchanges, one per device so that they run in call order."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    stream = _exchange_streams.get(index)
+    if stream is None:
+        stream = _exchange_streams[index] = torch.cuda.Stream(device)
+    return stream
+
+
 class ColumnShardedLinear:
     def __init__(self, b_prepacked, scale, bias, rank, world, device, group=None, exchange="all_gather"):
-        if exchange not in ("all_gather", "peer_store", "none"):
+        if exchange not in ("all_gather", "peer_store", "copy_engine", "none"):
             raise ValueError(f"unknown exchange {exchange!r}")
         self.rank, self.world, self.group = rank, world, group
         self.exchange = exchange
         self._symm = {}
+        self._exchange_done = {}
+        self._last_done = None
         self.n_total = b_prepacked.shape[1]
         self.k = b_prepacked.shape[0] * 16
         self.b_local, self.bias_local = shard_columns(b_prepacked.to(device), bias.to(device) if bias is not None else None, rank, world)
@@ -89,6 +111,15 @@ class ColumnShardedLinear:
         # the heuristic sees the full N so that a shard picks the variant (in particular the K split) of the whole
         self._variant_shape_n = self.n_total
         self.launches_per_call = 1
+
+    def with_exchange(self, exchange):
+        """The same weight shard behind another exchange (buffers of its own)."""
+        if exchange not in ("all_gather", "peer_store", "copy_engine", "none"):
+            raise ValueError(f"unknown exchange {exchange!r}")
+        other = object.__new__(ColumnShardedLinear)
+        other.__dict__.update(self.__dict__)
+        other.exchange, other._symm, other._exchange_done, other._last_done = exchange, {}, {}, None
+        return other
 
     def _variant(self, m, variant):
         if variant is not None:
@@ -123,11 +154,54 @@ class ColumnShardedLinear:
         handle.barrier()                       # every rank's blocks have landed everywhere
         return buf
 
-    def __call__(self, a, out_dtype, variant=None):
+    def _copy_engine(self, a, out_dtype, variant, defer):
+        m = a.shape[0]
+        key = (m, out_dtype)
+        bufs = self._symm.get(key)
+        if bufs is None:
+            bufs = self._symm[key] = _SymmetricBuffers((m, self.n_total), out_dtype, a.device, self.rank, self.world, self.group)
+        parity = bufs.calls & 1
+        buf, handle, views = bufs.next()
+        lo, hi = self.rank * self.n_local, (self.rank + 1) * self.n_local
+        compute = torch.cuda.current_stream(a.device)
+        side = exchange_stream(a.device)
+        # The copies that read this buffer two calls ago must be done before the GEMM overwrites the block.
+        previous = self._exchange_done.get((key, parity))
+        if previous is not None:
+            compute.wait_event(previous)
+        block = buf[:, lo:hi]
+        native.scaled_mm_into(a, self.b_local, self.scale, self.bias_local, block, variant=self._variant(m, variant))
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        side.wait_event(ready)
+        # A peer's buffer of this parity may be overwritten once that peer has run every reader of its previous contents.
+        # The readers precede the peer's previous call of this linear on its compute stream; that call's barrier follows
+        # its GEMM; and these copies follow this rank's side of that barrier on the exchange stream.
+        for i in range(1, self.world):                 # rotated order: at any moment the ranks' copies head for different GPUs
+            peer = (self.rank + i) % self.world
+            native.copy_block_into(views[peer][:, lo:hi], block, stream=side)
+        with torch.cuda.stream(side):
+            handle.barrier()                           # every rank's blocks have landed everywhere
+        done = torch.cuda.Event()
+        done.record(side)
+        self._exchange_done[(key, parity)] = done
+        self._last_done = done
+        if not defer:
+            compute.wait_event(done)
+        return buf
+
+    def wait_exchange(self, stream=None):
+        """Orders `stream` (default: the current one) after the exchange of the last deferred call."""
+        if self._last_done is not None:
+            (stream if stream is not None else torch.cuda.current_stream()).wait_event(self._last_done)
+
+    def __call__(self, a, out_dtype, variant=None, defer=False):
         if self.exchange == "none":
             return self.gemm_only(a, out_dtype, variant)
         if self.world > 1 and self.exchange == "peer_store":
             return self._peer_store(a, out_dtype, variant)
+        if self.world > 1 and self.exchange == "copy_engine":
+            return self._copy_engine(a, out_dtype, variant, defer)
         local = self.gemm_only(a, out_dtype, variant)
         if self.world == 1:
             return local

@@ -178,6 +178,15 @@ FEATHER_API int feather_reduce_partials(const void* partials, int n_src, int64_t
                                         int64_t ld_res, void* const* dst_list_host, int n_dst, int64_t ld_dst, int dtype,
                                         feather_stream_t stream);
 
+/* Strided block copy by a copy engine (no SM time): `rows` rows of `width_bytes` bytes from src (row pitch src_pitch_bytes) to
+ * dst (row pitch dst_pitch_bytes), device to device, asynchronous on `stream`.  dst may be peer-mapped memory of another GPU
+ * of the box: this is how a column-sharded linear hands its finished [M, N/g] block to the other ranks' [M, N] outputs on a
+ * second stream while the next linear's GEMM has the SMs (feather_scaled_mm_multi instead overlaps the transfer with the
+ * same linear's tiles).  The copy is a store as seen from this GPU: nothing is loaded from peer memory.  The reference has no
+ * multi-GPU path; this entry point has no counterpart in the reference. */
+FEATHER_API int feather_copy_block(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t width_bytes,
+                                   int64_t rows, feather_stream_t stream);
+
 /* Scratch bytes the variant chosen for (M,N,K) needs (0 when it does not split K; for the streaming kernel an upper bound of
  * what a K split across CTAs may use - with less, or none, it splits less, or not at all).  Pass the same
  * `variant` (or NULL) as to feather_scaled_mm_ex.  The reference's shipped kernel never splits K (README.md:31

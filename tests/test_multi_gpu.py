@@ -1,6 +1,6 @@
-"""GPU (2 or more devices): the sharded linears and the DiT harness, one process per GPU over NCCL / NVLink.  Both exchanges of
-the column-sharded linear - the fused peer-store epilogue over symmetric memory and the NCCL all-gather baseline - must
-reproduce the single-GPU output bit for bit (K is never split across ranks); the row-parallel linear (K split) must be within
+"""GPU (2 or more devices): the sharded linears and the DiT harness, one process per GPU over NCCL / NVLink.  All exchanges of
+the column-sharded linear - the fused peer-store epilogue over symmetric memory, the copy-engine push on a second stream and
+the NCCL all-gather baseline - must reproduce the single-GPU output bit for bit (K is never split across ranks); the row-parallel linear (K split) must be within
 the GEMM gate and identical on all ranks; the DiT forward is bitwise in all-gather mode and within 2e-2 (Frobenius) in pairs
 mode.  Skipped on a single-GPU box."""
 
@@ -52,12 +52,24 @@ def _worker(rank, world, port, tmpdir):
     s = s.reshape(1)
     full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     native.scaled_mm_into(a, bq, s, bias, full)
-    for exchange in ("peer_store", "all_gather"):
+    for exchange in ("peer_store", "copy_engine", "all_gather"):
         lin = sharded.ColumnShardedLinear(bq, s, bias, rank, world, dev, exchange=exchange)
         for call in range(3):                                 # three calls: both halves of the double-buffered output are reused
             out = lin(a, torch.bfloat16)
             torch.cuda.synchronize()
             check(f"column {exchange} call {call}", out.shape == (M, N) and torch.equal(out.view(torch.int16), full.view(torch.int16)))
+    # copy-engine exchange, deferred: five calls in a row return before their exchanges have run (each buffer is reused while
+    # older exchanges are still queued on the second stream); a reader orders itself with wait_exchange()
+    lin = sharded.ColumnShardedLinear(bq, s, bias, rank, world, dev, exchange="copy_engine")
+    kept = []
+    for call in range(5):
+        out = lin(a, torch.bfloat16, defer=True)
+        if call >= 3:
+            lin.wait_exchange()
+            kept.append(out.clone())                          # read in stream order, before the next call may overwrite a buffer
+    torch.cuda.synchronize()
+    for i, out in enumerate(kept):
+        check(f"column copy_engine deferred read {i}", torch.equal(out.view(torch.int16), full.view(torch.int16)))
     # 256-token pair tiles with two staging buffers per epilogue group (what the benchmark shapes use), ragged last tile
     M3 = 8192 + 136                                           # 99 pair tiles per rank: some CTA pairs run two tiles through the ring
     a3 = torch.randn((M3, K), generator=g, device=dev).to(torch.float16)
