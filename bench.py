@@ -619,12 +619,15 @@ def run_e2e_sharded(layers, native, odt, dev, world, rank, flops_step, steps, va
                 ev_in.record(s_in)
             with torch.cuda.stream(s_mm):
                 s_mm.wait_event(ev_in)
-                out = lin(full, odt, variant=variant)
+                deferred = lin.exchange == "copy_engine"
+                out = lin(full, odt, variant=variant, defer=True) if deferred else lin(full, odt, variant=variant)
                 ev_mm = torch.cuda.Event()
                 ev_mm.record(s_mm)
                 done[li] = ev_mm
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_mm)
+                if deferred:
+                    lin.wait_exchange(s_out)                  # the download waits for the peers' blocks, the next GEMM does not
                 hc.copy_(out[r0:r0 + rows], non_blocking=True)
                 ev_out = torch.cuda.Event()
                 ev_out.record(s_out)
