@@ -18,7 +18,8 @@ The N = 1 line also carries `small_m`: GB/s of the bandwidth-bound shapes (M in 
 
 Other workloads (not the driver's line): --workload qwen | smallm | quant | dit, or --shape M,N,K for a single GEMM.
 `--workload dit` is the 4-block Wan-like DiT forward (32768 tokens) whose linears are all Feather linears; `--dit-mode pairs`
-runs it as tensor-parallel pairs (column-parallel -> row-parallel) instead of an all-gather after every linear.
+runs it as tensor-parallel pairs (column-parallel -> row-parallel) instead of an all-gather after every linear, `--dit-mode
+tokens` with token rows sharded and weights replicated (no exchange in the linears, keys and values all-gathered per block).
 """
 
 import argparse
@@ -116,7 +117,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wan", choices=["wan", "qwen", "smallm", "quant", "dit", "lora"])
-    ap.add_argument("--dit-mode", default="all_gather", choices=["all_gather", "pairs"])
+    ap.add_argument("--dit-mode", default="all_gather", choices=["all_gather", "pairs", "tokens"])
     ap.add_argument("--tokens", type=int, default=32768, help="dit: token count")
     ap.add_argument("--blocks", type=int, default=4, help="dit: transformer blocks")
     ap.add_argument("--no-small-m", action="store_true", help="skip the small_m sub-record of the default N = 1 line")
@@ -774,6 +775,8 @@ def run_dit(args, native, dev, world, rank, local):
     for _ in range(3):
         for name, _, a16 in captured:
             kw = {"residual": x} if (args.dit_mode == "pairs" and name in ("o", "down")) else {}
+            if args.dit_mode == "tokens":
+                kw = {"total_rows": T}
             blk[name](a16, torch.bfloat16, **kw)
     k1.record()
     torch.cuda.synchronize()
@@ -788,7 +791,8 @@ def run_dit(args, native, dev, world, rank, local):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16 activations; linears fp16xfp8e5m2->fp32->bf16", "data": "synthetic",
             "config": {"workload": f"{cfg.blocks}-block Wan-like DiT forward, {T} tokens, hidden {cfg.hidden}, {cfg.heads}x{cfg.head_dim} heads, FFN {cfg.ffn} GELU, RMSNorm, torch SDPA",
-                       "mode": args.dit_mode, "exchange": args.exchange if args.dit_mode == "all_gather" else "reduce-scatter fused into the row-parallel GEMM + reduce/all-gather kernel",
+                       "mode": args.dit_mode, "exchange": {"all_gather": args.exchange, "pairs": "reduce-scatter fused into the row-parallel GEMM + reduce/all-gather kernel",
+                                                                "tokens": "token rows sharded, weights replicated: no exchange in any linear; keys and values all-gathered per block by copy engines"}[args.dit_mode],
                        "l2": "activations of one block exceed the 126 MB L2 many times over; no flush needed"},
             "flops": {"linears": lin_flops, "attention": attn_flops},
             "linears": {"ms_per_block_with_exchange": lin_ms_block, "tflops_whole_job": lin_flops / cfg.blocks / (lin_ms_block * 1e-3) / 1e12,

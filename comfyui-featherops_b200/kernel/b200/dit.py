@@ -22,6 +22,13 @@ Multi-GPU modes (one process per GPU, the same seeded weights generated on every
                    of six, attention divided by the number of ranks.  Not bitwise (K is split across ranks): within the
                    GEMM gate per linear, tolerance end to end.
 
+    "tokens"       token rows sharded, weights replicated (an e5m2 weight is small against the activations): every linear is
+                   a local GEMM over the rank's T/g rows with no exchange at all; the one thing that needs every token,
+                   attention's keys and values, is all-gathered per block by copy engines while the value and query
+                   projections run.  Half the bytes of "pairs", none of them on the critical path of a linear.  Every linear
+                   is bitwise the 1-GPU linear on the same input; attention runs on another query partition, so the forward
+                   is compared within tolerance.
+
 `linear_factory` exists so tests can run the same forward on CPU ranks with the CPU oracle standing in for the CUDA GEMM;
 the default factory is the CUDA path and raises without a GPU.
 """
@@ -32,7 +39,7 @@ import torch
 import torch.nn.functional as F
 
 from . import native
-from .sharded import ColumnShardedLinear, RowShardedLinear
+from .sharded import ColumnShardedLinear, ReplicatedLinear, RowGather, RowShardedLinear
 
 
 @dataclass
@@ -74,6 +81,22 @@ class CudaLinearFactory:
         q, s = self._quantised(w)
         return RowShardedLinear(q, s, bias.to(torch.bfloat16), self.rank, self.world, self.device, group=self.group)
 
+    def full(self, w, bias):
+        q, s = self._quantised(w)
+        return ReplicatedLinear(q, s, bias.to(torch.bfloat16), self.device)
+
+    def row_gather(self, total_rows, cols, dtype):
+        return RowGather(total_rows, cols, dtype, self.device, self.rank, self.world, self.group)
+
+    def gather_rows(self, local_rows):
+        """[T/g, C] on every rank -> [T, C] on every rank (the forward's result)."""
+        if self.world == 1:
+            return local_rows
+        import torch.distributed as dist
+        out = torch.empty((self.world * local_rows.shape[0], local_rows.shape[1]), dtype=local_rows.dtype, device=local_rows.device)
+        dist.all_gather_into_tensor(out, local_rows.contiguous(), group=self.group)
+        return out
+
 
 def rmsnorm(x, gain, eps):
     return F.rms_norm(x, (x.shape[-1],), gain, eps)
@@ -82,7 +105,7 @@ def rmsnorm(x, gain, eps):
 class FeatherDiT:
     def __init__(self, cfg, rank=0, world=1, device=None, mode="all_gather", exchange="peer_store", seed=0, linear_factory=None,
                  init_device=None, group=None):
-        if mode not in ("all_gather", "pairs"):
+        if mode not in ("all_gather", "pairs", "tokens"):
             raise ValueError(f"unknown mode {mode!r}")
         if cfg.hidden != cfg.heads * cfg.head_dim:
             raise ValueError("hidden must equal heads x head_dim")
@@ -96,6 +119,7 @@ class FeatherDiT:
         gen = torch.Generator(device=init_device).manual_seed(seed)
         h, f = cfg.hidden, cfg.ffn
         pairs = mode == "pairs"
+        self._gathers = {}
 
         def weight(n, k):
             return torch.randn((n, k), generator=gen, device=init_device, dtype=torch.float32) / k ** 0.5
@@ -109,11 +133,16 @@ class FeatherDiT:
             b["norm1"] = (1.0 + vector(h, 0.1)).to(self.device, torch.bfloat16)
             b["norm2"] = (1.0 + vector(h, 0.1)).to(self.device, torch.bfloat16)
             q_gain, k_gain = (1.0 + vector(h, 0.1)), (1.0 + vector(h, 0.1))
-            for name, n, k in (("q", h, h), ("k", h, h), ("v", h, h)):
-                b[name] = self.factory.column(weight(n, k), vector(n, 0.1), gather=not pairs)
-            b["o"] = self.factory.row(weight(h, h), vector(h, 0.1)) if pairs else self.factory.column(weight(h, h), vector(h, 0.1))
-            b["up"] = self.factory.column(weight(f, h), vector(f, 0.1), gather=not pairs)
-            b["down"] = self.factory.row(weight(h, f), vector(h, 0.1)) if pairs else self.factory.column(weight(h, f), vector(h, 0.1))
+            if mode == "tokens":
+                # the same draws in the same order as the other modes, every weight whole
+                for name, n, k in (("q", h, h), ("k", h, h), ("v", h, h), ("o", h, h), ("up", f, h), ("down", h, f)):
+                    b[name] = self.factory.full(weight(n, k), vector(n, 0.1))
+            else:
+                for name, n, k in (("q", h, h), ("k", h, h), ("v", h, h)):
+                    b[name] = self.factory.column(weight(n, k), vector(n, 0.1), gather=not pairs)
+                b["o"] = self.factory.row(weight(h, h), vector(h, 0.1)) if pairs else self.factory.column(weight(h, h), vector(h, 0.1))
+                b["up"] = self.factory.column(weight(f, h), vector(f, 0.1), gather=not pairs)
+                b["down"] = self.factory.row(weight(h, f), vector(h, 0.1)) if pairs else self.factory.column(weight(h, f), vector(h, 0.1))
             # per-head gains of the q/k norm, [heads, head_dim]; a rank in pairs mode keeps the gains of its own heads
             heads = slice(rank * cfg.heads // world, (rank + 1) * cfg.heads // world) if pairs else slice(None)
             b["q_gain"] = q_gain.view(cfg.heads, cfg.head_dim)[heads].to(self.device, torch.bfloat16)
@@ -133,9 +162,53 @@ class FeatherDiT:
         out = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0))
         return out.squeeze(0).transpose(0, 1).reshape(t, -1)
 
+    def _forward_tokens(self, x, hook):
+        """Token rows sharded, weights replicated: x [T, hidden] (the same on every rank) -> [T, hidden] on every rank."""
+        cfg, bf16 = self.cfg, torch.bfloat16
+        cast = self.factory.to_fp16
+        t, d = x.shape[0], cfg.head_dim
+        if t % self.world:
+            raise ValueError(f"{t} tokens do not divide over {self.world} ranks")
+        rows = t // self.world
+        xl = x[self.rank * rows:(self.rank + 1) * rows]
+        gathers = self._gathers.get(t)
+        if gathers is None:
+            gathers = self._gathers[t] = (self.factory.row_gather(t, cfg.hidden, bf16), self.factory.row_gather(t, cfg.hidden, bf16))
+        k_all, v_all = gathers
+
+        def call(lin, name, i, a16, **kw):
+            y = lin(a16, bf16, total_rows=t, **kw)
+            if hook is not None:
+                hook(name, i, a16, y)
+            return y
+
+        for i, blk in enumerate(self.blocks):
+            h16 = cast(rmsnorm(xl, blk["norm1"], cfg.eps))
+            # keys first (normalised per head before they travel), then values, each on its way while the next projection runs
+            k = call(blk["k"], "k", i, h16)
+            k_rows = k_all.begin()
+            torch.mul(F.rms_norm(k.view(rows, -1, d), (d,), None, cfg.eps), blk["k_gain"], out=k_rows.view(rows, -1, d))
+            k_all.push()
+            v_rows = v_all.begin()
+            call(blk["v"], "v", i, h16, out=v_rows)
+            v_all.push()
+            q = call(blk["q"], "q", i, h16)
+            q = F.rms_norm(q.view(rows, -1, d), (d,), None, cfg.eps) * blk["q_gain"]
+            kf = k_all.wait().view(t, -1, d)
+            vf = v_all.wait().view(t, -1, d)
+            attn = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kf.transpose(0, 1).unsqueeze(0), vf.transpose(0, 1).unsqueeze(0))
+            attn16 = cast(attn.squeeze(0).transpose(0, 1).reshape(rows, -1))
+            xl = call(blk["o"], "o", i, attn16, residual=xl)
+            h16 = cast(rmsnorm(xl, blk["norm2"], cfg.eps))
+            u16 = cast(F.gelu(call(blk["up"], "up", i, h16), approximate="tanh"))
+            xl = call(blk["down"], "down", i, u16, residual=xl)
+        return self.factory.gather_rows(xl)
+
     def forward(self, x, hook=None):
         """x [T, hidden] bf16 (the same on every rank) -> [T, hidden] bf16 (the same on every rank).
         `hook(name, block, input_fp16, output)` sees every linear's input and output (tests use it)."""
+        if self.mode == "tokens":
+            return self._forward_tokens(x, hook)
         cfg, bf16 = self.cfg, torch.bfloat16
         pairs = self.mode == "pairs"
         cast = self.factory.to_fp16

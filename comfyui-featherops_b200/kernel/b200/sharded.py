@@ -32,6 +32,13 @@ RowShardedLinear      rank r keeps the k16-planes [r*K/16g, (r+1)*K/16g) (dim 0,
                       the single-GPU result: the partials are rounded to 16 bits before they are summed.  It is deterministic
                       (same bits on every rank, every run) and within the GEMM gate of the tests.
 
+ReplicatedLinear      the whole weight on every rank (an e5m2 weight is small against the activations it multiplies); rank r
+                      multiplies its own token rows and nothing is exchanged.  The launch takes the tile class of the launch
+                      over all tokens, so a row has the same bits on any number of ranks.
+RowGather             the all-gather that a token-sharded model needs where an operation reads every token (attention's keys and
+                      values): every rank writes its rows into its own [T, C] symmetric buffer, copy engines push them into
+                      the peers' buffers on the exchange stream, one cross-rank barrier there; `wait()` orders the reader.
+
 Only stores ever cross NVLink; no load reads peer memory.  With world size 1 there is no exchange and no copy.
 """
 
@@ -260,3 +267,81 @@ class RowShardedLinear:
         native.reduce_partials_into(part, self.bias, residual[lo:hi] if residual is not None else None, [out_views[r][lo:hi] for r in order])
         out_handle.barrier()                   # every rank's rows have landed everywhere
         return out
+
+
+class ReplicatedLinear:
+    """y = x @ W (+ bias, + residual) on this rank's token rows, the whole weight on every rank: no exchange."""
+
+    def __init__(self, b_prepacked, scale, bias, device):
+        self.b = b_prepacked.to(device)
+        self.n = self.b.shape[1]
+        self.k = self.b.shape[0] * 16
+        self.scale = scale.to(device=device, dtype=torch.float32)
+        self.bias = bias.to(device) if bias is not None else None
+        self.launches_per_call = 1
+
+    def __call__(self, a_rows, out_dtype, total_rows=None, residual=None, variant=None, out=None):
+        m = a_rows.shape[0]
+        if out is None:
+            out = torch.empty((m, self.n), dtype=out_dtype, device=a_rows.device)
+        if variant is None and total_rows is not None and total_rows != m:
+            # the tile class (and K split) of the launch over all tokens: every row then sees the additions of that launch
+            variant = native.choose_variant(total_rows, self.n, self.k)
+        native.scaled_mm_into(a_rows, self.b, self.scale, self.bias, out, variant=variant)
+        if residual is not None:
+            out += residual
+        return out
+
+
+class RowGather:
+    """All-gather of token rows into a [total_rows, cols] buffer on every rank: `begin()` returns this rank's rows of the next
+    buffer for the caller to fill on the compute stream, `push()` sends them to the peers (copy engines, exchange stream,
+    then the cross-rank barrier), `wait()` makes the current stream wait and returns the full buffer.  Buffers are
+    double-buffered: a rank's readers of buffer p precede its next begin() on the compute stream, that call's push follows
+    on the exchange stream, and only after its barrier do the peers' copies of the call after it arrive."""
+
+    def __init__(self, total_rows, cols, dtype, device, rank, world, group=None):
+        if total_rows % world != 0:
+            raise ValueError(f"{total_rows} token rows do not divide over {world} ranks")
+        self.rank, self.world, self.device = rank, world, device
+        self.rows = total_rows // world
+        self.bufs = _SymmetricBuffers((total_rows, cols), dtype, device, rank, world, group) if world > 1 else None
+        self.local = torch.empty((total_rows, cols), dtype=dtype, device=device) if world == 1 else None
+        self._done = [None, None]
+        self._cur = None
+
+    def begin(self):
+        if self.world == 1:
+            return self.local
+        parity = self.bufs.calls & 1
+        if self._done[parity] is not None:         # the copies that read these rows two calls ago are done
+            torch.cuda.current_stream(self.device).wait_event(self._done[parity])
+        self._cur = (parity,) + self.bufs.next()
+        lo = self.rank * self.rows
+        return self._cur[1][lo:lo + self.rows]
+
+    def push(self):
+        if self.world == 1:
+            return
+        parity, buf, handle, views = self._cur
+        lo = self.rank * self.rows
+        compute, side = torch.cuda.current_stream(self.device), exchange_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        side.wait_event(ready)
+        mine = buf[lo:lo + self.rows]
+        for i in range(1, self.world):
+            peer = (self.rank + i) % self.world
+            native.copy_block_into(views[peer][lo:lo + self.rows], mine, stream=side)
+        with torch.cuda.stream(side):
+            handle.barrier()
+        done = torch.cuda.Event()
+        done.record(side)
+        self._done[parity] = done
+
+    def wait(self):
+        if self.world == 1:
+            return self.local
+        parity, buf, _, _ = self._cur
+        torch.cuda.current_stream(self.device).wait_event(self._done[parity])
+        return buf

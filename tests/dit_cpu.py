@@ -18,9 +18,13 @@ class CpuOracleFactory:
         q, s = naive_torch.quantize_prepack_cpu(w.to("cpu", torch.float32))
         b = bias.to("cpu", torch.bfloat16)
 
-        def lin(a16, out_dtype, residual=None, variant=None):
+        def lin(a16, out_dtype, residual=None, variant=None, total_rows=None, out=None):
             y = naive_torch.scaled_mm_cpu(a16, q, s, b, out_dtype)
-            return y + residual if residual is not None else y
+            y = y + residual if residual is not None else y
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
 
         lin.q, lin.s, lin.b = q, s, b
         return lin
@@ -30,6 +34,36 @@ class CpuOracleFactory:
 
     def row(self, w, bias):
         return self._linear(w, bias)
+
+    def full(self, w, bias):
+        return self._linear(w, bias)
+
+    def row_gather(self, total_rows, cols, dtype):
+        return CpuRowGather(total_rows, cols, dtype, 0, 1)
+
+    def gather_rows(self, local_rows):
+        return local_rows
+
+
+class CpuRowGather:
+    """Same interface as kernel.b200.sharded.RowGather; the exchange is a gloo all-gather at wait()."""
+
+    def __init__(self, total_rows, cols, dtype, rank, world):
+        self.rank, self.world, self.rows = rank, world, total_rows // world
+        self.full = torch.empty((total_rows, cols), dtype=dtype)
+
+    def begin(self):
+        return self.full[self.rank * self.rows:(self.rank + 1) * self.rows]
+
+    def push(self):
+        pass
+
+    def wait(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            mine = self.full[self.rank * self.rows:(self.rank + 1) * self.rows].clone()
+            dist.all_gather_into_tensor(self.full, mine)
+        return self.full
 
 
 class GlooShardedFactory:
@@ -51,3 +85,15 @@ class GlooShardedFactory:
 
     def row(self, w, bias):
         raise NotImplementedError("the row-parallel linear exchanges through CUDA symmetric memory; it has no CPU stand-in")
+
+    def full(self, w, bias):
+        return CpuOracleFactory._linear(w, bias)
+
+    def row_gather(self, total_rows, cols, dtype):
+        return CpuRowGather(total_rows, cols, dtype, self.rank, self.world)
+
+    def gather_rows(self, local_rows):
+        import torch.distributed as dist
+        out = torch.empty((self.world * local_rows.shape[0], local_rows.shape[1]), dtype=local_rows.dtype)
+        dist.all_gather_into_tensor(out, local_rows.contiguous())
+        return out

@@ -68,6 +68,17 @@ def test_pairs_mode_on_one_gpu_is_the_same_forward(pkg, native, cuda_dev):
     assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
 
 
+def test_tokens_mode_on_one_gpu_is_the_same_forward(pkg, native, cuda_dev):
+    """With one rank the token-sharded mode runs the same linears on all rows and attention on all queries: bitwise equal."""
+    cfg_kwargs = dict(hidden=1024, heads=8, head_dim=128, ffn=2816, blocks=2)
+    cfg, a, _ = _models(pkg, cuda_dev, cfg_kwargs, mode="all_gather")
+    _, b, _ = _models(pkg, cuda_dev, cfg_kwargs, mode="tokens")
+    x = torch.randn((384, cfg.hidden), generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).to(cuda_dev)
+    ya, yb = a(x), b(x)
+    native.check_device_status(cuda_dev)
+    assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
+
+
 def test_harness_linear_is_the_operator_linear(pkg, native, cuda_dev):
     """A linear of the harness gives bit for bit what `FeatherOps.Linear` (the ComfyUI operator, here under the test double
     of `comfy`) gives for the same fp32 weight, bias and bf16 input."""

@@ -173,8 +173,17 @@ def _dit_worker(rank, world, port, tmpdir):
     y, ref = model(x), single(x)
     ok = y.shape == ref.shape and torch.equal(y.view(torch.int16), ref.view(torch.int16))
     shards_ok = all(lin.n_local * world == lin.n_total for _, _, lin in model.linears())
+    # token rows sharded, weights replicated, keys and values all-gathered per block: the same linears on the same rows, attention
+    # on this rank's queries only, so the forward agrees within rounding (bit for bit where the attention kernel is row-wise)
+    tokens = dit.FeatherDiT(cfg, rank=rank, world=world, device=cpu, mode="tokens", seed=2, init_device=cpu,
+                            linear_factory=GlooShardedFactory(rank, world, sharded))
+    yt = tokens(x)
+    fro = float((yt.float() - ref.float()).norm() / ref.float().norm())
+    gathered = [torch.empty_like(yt) for _ in range(world)]
+    dist.all_gather(gathered, yt.contiguous())
+    tokens_ok = yt.shape == ref.shape and fro <= 1e-2 and all(torch.equal(g.view(torch.int16), gathered[0].view(torch.int16)) for g in gathered)
     with open(os.path.join(tmpdir, f"ok{rank}"), "w") as f:
-        f.write("1" if ok and shards_ok else "0")
+        f.write("1" if ok and shards_ok and tokens_ok else f"0 all_gather={ok} shards={shards_ok} tokens={tokens_ok} fro={fro:.3e}")
     dist.destroy_process_group()
 
 

@@ -113,6 +113,28 @@ def _worker(rank, world, port, tmpdir):
     fro = float((yp.float() - one.float()).norm() / one.float().norm())
     check(f"dit pairs fro_rel {fro:.3e}", fro <= 2e-2)
     check("dit pairs identical on all ranks", same_on_all_ranks(yp))
+    # token rows sharded, weights replicated, keys/values all-gathered by copy engines: every linear is bitwise the one-rank linear
+    # on the same rows (checked through the hook against a launch over the same rows with the full-size variant); the forward is
+    # within tolerance (attention runs on another query partition) and identical on all ranks.  Two forwards: the gather
+    # buffers are reused.
+    tok = dit.FeatherDiT(cfg, rank=rank, world=world, device=dev, mode="tokens", seed=3)
+    seen = []
+    yt = tok(x, hook=lambda name, i, a16, y: seen.append((name, i, a16, y.clone())))
+    yt2 = tok(x).clone()
+    torch.cuda.synchronize()
+    fro = float((yt.float() - one.float()).norm() / one.float().norm())
+    check(f"dit tokens fro_rel {fro:.3e}", yt.shape == one.shape and fro <= 2e-2)
+    check("dit tokens identical on all ranks", same_on_all_ranks(yt))
+    check("dit tokens second forward identical", torch.equal(yt.view(torch.int16), yt2.view(torch.int16)))
+    bitwise = True
+    for name, i, a16, y in seen:
+        lin = tok.blocks[i][name]
+        ref = torch.empty_like(y)
+        native.scaled_mm_into(a16, lin.b, lin.scale, lin.bias, ref, variant=native.choose_variant(x.shape[0], lin.n, lin.k))
+        if name in ("o", "down"):
+            continue                                          # these carry the residual; their GEMM is the same launch as the others'
+        bitwise = bitwise and torch.equal(ref.view(torch.int16), y.view(torch.int16))
+    check("dit tokens linears bitwise", bitwise and len(seen) == 6 * cfg.blocks)
     native.check_device_status(dev)
     with open(os.path.join(tmpdir, f"ok{rank}"), "w") as f:
         f.write("ok" if not failed else "FAILED: " + "; ".join(failed))
