@@ -345,6 +345,7 @@ def run_ours(args):
     # The exchanged outputs are checked before anything is timed: on every rank, rows of each [M, N] output against an unsharded
     # GEMM of the same rows on that rank (K is never split, so they must agree bit for bit); MIN over the ranks.
     exchange_check = None
+    token_sharded = None
     if world > 1:
         rows_checked, equal = 0, True
         for a, lin, K, N, bq_full in layers:
@@ -360,6 +361,29 @@ def run_ours(args):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         exchange_check = {"bitwise_equal": bool(flag.item()), "layers": len(layers), "rows": rows_checked, "ranks": world,
                           "what": "rows of every exchanged [M,N] output on every rank against an unsharded GEMM of the same rows on that rank"}
+        # The same step sharded by token rows instead (weights whole on every rank, M/g rows each, nothing exchanged, every rank
+        # ends with its rows of the outputs): the data-parallel form of the path, reported beside the column-sharded line.
+        rows = M // world
+        replicated = [(a[rank * rows:(rank + 1) * rows], sharded.ReplicatedLinear(bq_full, lin.scale, None, dev), torch.empty((rows, N), dtype=odt, device=dev))
+                      for a, lin, K, N, bq_full in layers]
+        for _ in range(args.warmup):
+            for a_rows, rl, out in replicated:
+                rl(a_rows, odt, total_rows=M, out=out)
+        torch.cuda.synchronize()
+        dist.barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(args.steps):
+            for a_rows, rl, out in replicated:
+                rl(a_rows, odt, total_rows=M, out=out)
+        r1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([r0.elapsed_time(r1) / args.steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        token_sharded = {"ms_per_step": float(t.item()), "tflops": sum(2.0 * M * K * N for K, N in kn_list) / (float(t.item()) * 1e-3) / 1e12,
+                         "note": f"token rows sharded ({rows} per rank), weights replicated, no exchange; each rank keeps its rows of the outputs"}
+        del replicated
         for i in range(len(layers)):                       # the full weights were only needed for the check
             layers[i] = layers[i][:4] + (None,)
         torch.cuda.empty_cache()
@@ -512,6 +536,8 @@ def run_ours(args):
             line["exchange_check"] = exchange_check
         if exchange is not None:
             line["exchange"] = exchange
+        if token_sharded is not None:
+            line["token_sharded"] = token_sharded
         if small_m is not None:
             line["small_m"] = small_m
         print(json.dumps(line), flush=True)
