@@ -346,6 +346,7 @@ def run_ours(args):
     # GEMM of the same rows on that rank (K is never split, so they must agree bit for bit); MIN over the ranks.
     exchange_check = None
     token_sharded = None
+    e2e_rows = None
     if world > 1:
         rows_checked, equal = 0, True
         for a, lin, K, N, bq_full in layers:
@@ -383,8 +384,9 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         token_sharded = {"ms_per_step": float(t.item()), "tflops": sum(2.0 * M * K * N for K, N in kn_list) / (float(t.item()) * 1e-3) / 1e12,
                          "note": f"token rows sharded ({rows} per rank), weights replicated, no exchange; each rank keeps its rows of the outputs"}
+        e2e_rows = [(a_rows, sharded.ColumnShardedLinear(rl.b, rl.scale, None, 0, 1, dev), K, N, None) for (a_rows, rl, _), (_, _, K, N, _) in zip(replicated, layers)]
         del replicated
-        for i in range(len(layers)):                       # the full weights were only needed for the check
+        for i in range(len(layers)):                       # the full weights were only needed for the check (and the token-sharded legs)
             layers[i] = layers[i][:4] + (None,)
         torch.cuda.empty_cache()
         if not exchange_check["bitwise_equal"]:
@@ -509,6 +511,16 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         e2e = run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps=max(2, min(args.steps, 5)), variant=variant) if typed_outputs is None else None
+        if e2e is not None and e2e_rows is not None:
+            # Host buffers in, host buffers out needs no exchange at all when the ranks split the token rows: every rank uploads its
+            # M/g rows, multiplies them with the whole weights and downloads its rows of the outputs - nothing crosses NVLink.
+            # That is the end-to-end form of the job on N GPUs; the column-sharded one (all-gather of the uploaded rows, sharded
+            # linear, exchange) is kept beside it.
+            bound = bind_to_gpu_numa_node(dev)
+            rows_leg = run_e2e(e2e_rows, hk, native, odt, dev, 1, rank, flops_step / world, steps=max(2, min(args.steps, 5)), variant=None, all_ranks=world)
+            rows_leg["column_sharded"] = {k: e2e[k] for k in ("value", "note")}
+            rows_leg["host_binding_rank0"] = bound
+            e2e = rows_leg
 
     small_m = None
     if world == 1 and args.workload == "wan" and not args.shape and not args.no_small_m:
@@ -545,13 +557,40 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps, variant=None):
+def bind_to_gpu_numa_node(dev):
+    """Runs this process on the cores of the NUMA node the GPU hangs off, so that the pinned host buffers allocated afterwards
+    are first touched there and the copies do not cross the socket link.  Returns a short description, or None if the
+    topology cannot be read (then nothing changes)."""
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return f"numa node {node}, {len(allowed)} cores"
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
+def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps, variant=None, all_ranks=1):
     """The same step with HOST activations and outputs: H2D + kernel + D2H inside the timed region, every step.
 
     One GPU: through the operator `scaled_mm_hip`, each linear in four row chunks on copy-in / GEMM / copy-out streams.
-    Several GPUs: the host holds each activation once, so every rank uploads only its M/g rows and the rows are all-gathered
-    over NVLink (NCCL); the sharded linear runs; every rank downloads its M/g rows of the exchanged output.  The box as a
-    whole still moves every activation byte up and every output byte down, once, every step.
+    Several GPUs, two forms.  Token rows split over the ranks (`all_ranks` > 1: this function runs on every rank over its own
+    M/g rows with the whole weights, nothing is exchanged) is the line's `e2e`.  The column-sharded form (run_e2e_sharded:
+    every rank uploads its M/g rows, the rows are all-gathered over NVLink, the sharded linear runs with its exchange, every
+    rank downloads its M/g rows of the exchanged output) is reported beside it.  Either way the box as a whole moves every
+    activation byte up and every output byte down, once, every step.
     """
     import torch.distributed as dist
 
@@ -605,14 +644,24 @@ def run_e2e(layers, hk, native, odt, dev, world, rank, flops_step, steps, varian
 
     e2e_step()
     torch.cuda.synchronize()
+    if all_ranks > 1:
+        dist.barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
         e2e_step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     native.check_device_status(dev)
-    return {"value": flops_step * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "note": "weights stay resident on the GPU; activations come from and outputs return to pinned host memory every step, in 4 row chunks per linear on copy-in / GEMM / copy-out streams"}
+    note = "weights stay resident on the GPU; activations come from and outputs return to pinned host memory every step, in 4 row chunks per linear on copy-in / GEMM / copy-out streams"
+    if all_ranks > 1:
+        # every rank ran this over its own M/g token rows (whole weights, no exchange): the slowest rank's time counts
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        return {"value": flops_step * all_ranks * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * all_ranks, "d2h_bytes_per_step": d2h * all_ranks,
+                "h2d_bytes_per_step_per_rank": h2d, "d2h_bytes_per_step_per_rank": d2h,
+                "note": f"token rows split over the {all_ranks} ranks, weights whole on every rank, no exchange; " + note + "; bytes are totals over the ranks"}
+    return {"value": flops_step * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "note": note}
 
 
 def run_e2e_sharded(layers, native, odt, dev, world, rank, flops_step, steps, variant):
