@@ -79,9 +79,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples that arrived between t_begin and t_end (time.perf_counter values; the driver publishes a new
+        reading about every 100 ms, so a short region holds few distinct ones); of all samples when no window is given."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -91,7 +93,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = [(t, l) for t, l in self.lines if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end + 0.03)]
+        if not window:                       # a region shorter than the sampling period: take the readings nearest to it
+            window = self.lines[-2:]
+        for _, line in window:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -106,8 +111,8 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [c for c, p in zip(sm, pw) if p > 0.5 * max(pw)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "power_w_max": max(pw), "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(sm), "sm_mhz_min": min(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw), "samples": len(sm),
+                "reasons": sorted(reasons)}
 
 
 def parse_args():
@@ -404,6 +409,7 @@ def run_ours(args):
         dist.barrier()
     launch_events = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
         step(launch_events if world == 1 else None)
@@ -412,10 +418,13 @@ def run_ours(args):
             lin.wait_exchange()
     e1.record()
     torch.cuda.synchronize()
+    t_end = time.perf_counter()
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        time.sleep(0.12)                     # the reading that covers the end of the region is published up to 100 ms later
+    clocks = sampler.stop(t_begin, t_end + 0.1) if rank == 0 else None
     native.check_device_status(dev)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -822,15 +831,17 @@ def run_dit(args, native, dev, world, rank, local):
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
         y = model(x)
     e1.record()
     torch.cuda.synchronize()
+    t_end = time.perf_counter()
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     native.check_device_status(dev)
     if world > 1:
         t = torch.tensor([ms], device=dev)
