@@ -59,6 +59,13 @@ def test_bad_arguments_return_codes_without_a_device(native):
     assert lib.feather_dequantize(one, one, 16, 16, 5, one, null) in (1, 4)
     assert lib.feather_bf16_to_fp16(one, one, -1, null) == 1
     assert lib.feather_bf16_to_fp16(null, null, 0, null) == 0
+    assert lib.feather_copy_block(null, 64, one, 64, 32, 4, null) == 1
+    assert lib.feather_copy_block(one, 16, one, 64, 32, 4, null) == 1                            # pitch smaller than the width
+    assert b"pitch" in lib.feather_last_error_string()
+    assert lib.feather_copy_block(one, 64, one, 64, 0, 4, null) == 0                             # nothing to copy
+    ptrs = (ctypes.c_void_p * 1)(16)
+    assert lib.feather_reduce_partials(one, 0, 16, 64, null, null, 0, ptrs, 1, 64, 1, null) == 1    # n_src out of range
+    assert lib.feather_reduce_partials(one, 2, 16, 60, null, null, 0, ptrs, 1, 64, 1, null) == 1    # N not a multiple of 8
 
 
 def test_missing_library_fails_loudly(native, monkeypatch):
