@@ -735,7 +735,7 @@ def run_e2e_sharded(layers, native, odt, dev, world, rank, flops_step, steps, va
     return {"value": flops_step * steps / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
             "h2d_bytes_per_step_per_rank": h2d, "d2h_bytes_per_step_per_rank": d2h,
             "note": "weights stay resident; every step each rank uploads its M/g rows of every activation from pinned host memory, the rows are all-gathered over "
-                    "NVLink (NCCL), the sharded linear runs with the fused exchange, and each rank downloads its M/g rows of the output; bytes are totals over the ranks"}
+                    "NVLink (NCCL), the column-sharded linear runs with its exchange, and each rank downloads its M/g rows of the output; bytes are totals over the ranks"}
 
 
 def run_smallm(args, native, dev, Ms=(1, 8, 16, 64, 128), steps=None):
