@@ -18,7 +18,7 @@ There is no CPU implementation: a tensor that lives in host memory (a checkpoint
 current CUDA device, processed there and the result is returned on the tensor's original device.
 """
 
-from dataclasses import dataclass, fields
+from dataclasses import dataclass, fields, replace
 
 import comfy.float
 import torch
@@ -62,32 +62,30 @@ def unprepack_transpose(x):
 
 @dataclass(frozen=True)
 class FeatherFP8E5M2PackedParams:
+    """What a packed weight carries beside its bytes.  `QuantizedTensor` moves, clones and overwrites it through the three
+    methods below (the contract of the reference's class, comfy_feather/quant.py:22-49); `scale` is the only tensor."""
+
     scale: torch.Tensor
     orig_dtype: torch.dtype
     orig_shape: tuple[int, ...]
 
-    def _tensor_fields(self):
-        return ["scale"]
+    _TENSORS = ("scale",)
+
+    def _with_tensors(self, fn):
+        return replace(self, **{name: fn(getattr(self, name)) for name in self._TENSORS})
 
     def to_device(self, device):
-        kwargs = {f.name: getattr(self, f.name) for f in fields(self)}
-        for name in self._tensor_fields():
-            kwargs[name] = kwargs[name].to(device=device)
-        return type(self)(**kwargs)
+        return self._with_tensors(lambda t: t.to(device=device))
 
     def clone(self):
-        kwargs = {f.name: getattr(self, f.name) for f in fields(self)}
-        for name in self._tensor_fields():
-            kwargs[name] = kwargs[name].clone()
-        return type(self)(**kwargs)
+        return self._with_tensors(torch.Tensor.clone)
 
     def copy_from(self, src, non_blocking=False):
         for f in fields(self):
-            value = getattr(src, f.name)
-            if f.name in self._tensor_fields():
-                getattr(self, f.name).copy_(value, non_blocking=non_blocking)
+            if f.name in self._TENSORS:
+                getattr(self, f.name).copy_(getattr(src, f.name), non_blocking=non_blocking)
             else:
-                object.__setattr__(self, f.name, value)
+                object.__setattr__(self, f.name, getattr(src, f.name))            # frozen dataclass: the plain fields are replaced
 
 
 def _quantize_and_prepack(x, scale, seed, inplace_ops, premul=None):
