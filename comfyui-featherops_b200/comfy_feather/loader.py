@@ -1,12 +1,13 @@
 """ComfyUI node `FeatherUNetLoader` (reference: comfy_feather/loader.py:9-77): loads a diffusion model with
-`custom_operations = feather_ops(out_dtype, excluded_names)` so every eligible Linear becomes a Feather linear."""
+`custom_operations = feather_ops(out_dtype, excluded_names)` so every eligible Linear becomes a Feather linear.
+The reference's loader also installs a sampling-time model pin (comfy_feather/sampling.py:64-83), ComfyUI memory-management
+bookkeeping that is not part of the linear path and is not rebuilt here."""
 
 import folder_paths
 import torch
 from comfy.sd import load_diffusion_model
 
 from .ops import feather_ops
-from .sampling import install_sampling_model_pin
 
 # model_type -> (module-name fragments that stay un-quantised, GEMM output dtype).  Excluded are the non-repeating
 # input/output modules and, for qwen, the modulation layers fed by the time-embedding vector.
@@ -40,5 +41,4 @@ class FeatherUNetLoader:
         unet_path = folder_paths.get_full_path_or_raise("diffusion_models", unet_name)
         excluded, out_dtype = MODEL_TYPES.get(model_type, MODEL_TYPES["default"])
         model = load_diffusion_model(unet_path, model_options={"custom_operations": feather_ops(out_dtype=out_dtype, excluded_names=list(excluded))})
-        install_sampling_model_pin(model)
         return (model,)
