@@ -4,11 +4,13 @@
 // arithmetic is tiny.  The tcgen05 kernel is the wrong tool there (one thread issues eight MMAs per 16 KB of weights and
 // becomes the limit), so this kernel keeps everything in registers:
 //
-//   work item   P strips of 8 output columns n (P*8 n), all of K; P is picked so the items fill the SMs in as few, as full rounds as possible
+//   work item   P strips of output columns n, all of K; P is picked so the items fill the SMs in as few, as full rounds as possible
 //   CTA         16 warps; warp w takes the k16-blocks [w*KB/16, (w+1)*KB/16) of the item, so the K split needs no workspace
-//   per k16-block and strip: one 32-bit load per lane straight from the prepacked layout (a warp load is the 128 contiguous bytes
-//               of a strip), 2 x prmt (e5m2 -> fp16 is byte << 8), one mma.sync.m16n8k16 (tokens x n, fp32 accumulate)
-//               per 16-token tile; token fragments come from global/L1 and are reused across the P strips
+//   up to 16 tokens (small_m8_kernel): a strip is 16 columns; per k16-block and strip two 32-bit loads per lane straight from
+//               the prepacked layout (a warp load is 128 contiguous bytes), 4 x prmt (e5m2 -> fp16 is byte << 8) build the
+//               16 n x 16 k MMA operand once, and one mma.sync.m16n8k16 per group of eight tokens multiplies it (fp32
+//               accumulate); token fragments come from global/L1 and are reused across the P strips
+//   17..32 tokens, on request (small_m_kernel): a strip is 8 columns, the tokens are the 16-row operand, two tiles of them
 //   reduce      the 16 warps' fp32 partials go through shared memory and are added in warp order (deterministic), then
 //               * scale -> RTNE -> + bias in the output dtype, as in the tensor-memory kernel
 //
@@ -90,7 +92,9 @@ __device__ __forceinline__ uint16_t sm_finish(float acc, float scale, int out_mo
     return __half_as_ushort(v);
 }
 
-// MT: 16-token tiles (1 or 2); P: strips of 8 n per work item; U: k16-blocks whose loads are issued together.
+// MT: 16-token tiles (instantiated for 2: 17..32 tokens; up to 16 tokens take small_m8_kernel below, which builds each weight
+// fragment once for both groups of eight tokens and measured 5-14 % faster); P: strips of 8 n per work item; U: k16-blocks
+// whose loads are issued together.
 //
 // Inside a k16-block the MMA's k index is permuted (the sum over k does not care): MMA k = 2j, 2j+1 is physical
 // k = 4j, 4j+1 and MMA k = 2j+8, 2j+9 is physical k = 4j+2, 4j+3.  Lane (g, j) then needs exactly the aligned 32-bit word j
@@ -217,16 +221,18 @@ small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, co
     }
 }
 
-// Up to 8 tokens: the weights are the 16-row MMA operand (16 n x 16 k = 256 bytes of weights per MMA, half the MMAs of the
-// kernel above, which is bound by the legacy MMA rate) and the tokens the 8-column operand.  P: strips of 16 n per item.
-template <int P, int U>
+// Up to 8 * NT tokens (NT = 1 or 2): the weights are the 16-row MMA operand (16 n x 16 k = 256 bytes of weights per MMA and
+// token group) and each group of eight tokens the 8-column operand; the weight fragment of a strip is built once and
+// multiplied with every token group.  P: strips of 16 n per item.
+template <int P, int U, int NT>
 __global__ void __launch_bounds__(kSmThreads, 1)
 small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, const float* __restrict__ scale_ptr,
                 const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items,
                 SplitArgs sp) {
     constexpr int kCols = P * 16;
     constexpr int kPitch = kCols + 1;
-    extern __shared__ float red[];                          // [kSmWarps][8 tokens][kPitch]
+    constexpr int kTok = 8 * NT;
+    extern __shared__ float red[];                          // [kSmWarps][kTok tokens][kPitch]
     __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -244,16 +250,18 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
         const int kb_begin = sl_begin + static_cast<int>(static_cast<long long>(warp) * (sl_end - sl_begin) / kSmWarps);
         const int kb_end = sl_begin + static_cast<int>(static_cast<long long>(warp + 1) * (sl_end - sl_begin) / kSmWarps);
         const int n_base = group * kCols;
-        float acc[P][4];
+        float acc[NT][P][4];
 #pragma unroll
-        for (int s = 0; s < P; ++s)
+        for (int t = 0; t < NT; ++t)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[s][i] = 0.0f;
+            for (int s = 0; s < P; ++s)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[t][s][i] = 0.0f;
         // lane (g, j): word j of chunk g (rows 0-7 of a strip) and of chunk g + 8; a strip is 256 contiguous bytes
         const uint8_t* const w_lane = w + static_cast<long long>(n_base) * 16 + lane * 4;
         const long long plane = static_cast<long long>(N) * 16;
 
-        auto load_block = [&](int kb0, uint32_t (&wv)[U][P][2], uint2 (&tk)[U]) {
+        auto load_block = [&](int kb0, uint32_t (&wv)[U][P][2], uint2 (&tk)[U][NT]) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int kb = kb0 + u;
@@ -264,11 +272,14 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
                     wv[u][s][0] = (kb_ok && n0 < N) ? __ldg(reinterpret_cast<const uint32_t*>(w_lane + kb * plane + s * 256)) : 0u;
                     wv[u][s][1] = (kb_ok && n0 + 8 < N) ? __ldg(reinterpret_cast<const uint32_t*>(w_lane + kb * plane + s * 256 + 128)) : 0u;
                 }
-                tk[u] = (kb_ok && g < M) ? __ldg(reinterpret_cast<const uint2*>(a + g * static_cast<long long>(K) + static_cast<long long>(kb) * 16 + 4 * j))
-                                         : make_uint2(0u, 0u);
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    tk[u][t] = (kb_ok && g + 8 * t < M)
+                                   ? __ldg(reinterpret_cast<const uint2*>(a + (g + 8 * t) * static_cast<long long>(K) + static_cast<long long>(kb) * 16 + 4 * j))
+                                   : make_uint2(0u, 0u);
             }
         };
-        auto multiply_block = [&](const uint32_t (&wv)[U][P][2], const uint2 (&tk)[U]) {
+        auto multiply_block = [&](const uint32_t (&wv)[U][P][2], const uint2 (&tk)[U][NT]) {
 #pragma unroll
             for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -276,11 +287,12 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
                     // same k permutation as above: bytes 0,1 of the word are MMA k = 2j, 2j+1; bytes 2,3 are MMA k = 2j+8, 2j+9
                     const uint32_t frag[4] = {__byte_perm(wv[u][s][0], 0u, 0x1404), __byte_perm(wv[u][s][1], 0u, 0x1404),
                                               __byte_perm(wv[u][s][0], 0u, 0x3424), __byte_perm(wv[u][s][1], 0u, 0x3424)};
-                    mma_m16n8k16(acc[s], frag, tk[u].x, tk[u].y);
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) mma_m16n8k16(acc[t][s], frag, tk[u][t].x, tk[u][t].y);
                 }
         };
         uint32_t w0[U][P][2], w1[U][P][2];
-        uint2 t0[U], t1[U];
+        uint2 t0[U][NT], t1[U][NT];
         int kb0 = kb_begin;
         if (kb0 < kb_end) load_block(kb0, w0, t0);
         while (kb0 < kb_end) {
@@ -292,20 +304,22 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
             if (kb0 < kb_end) load_block(kb0, w0, t0);
             multiply_block(w1, t1);
         }
-        // D: d0 (n g, token 2j), d1 (n g, token 2j+1), d2 (n g+8, token 2j), d3 (n g+8, token 2j+1)
-        float* const mine = red + warp * (8 * kPitch);
+        // D of token group t: d0 (n g, token 8t + 2j), d1 (n g, token 8t + 2j+1), d2 (n g+8, token 8t + 2j), d3 (n g+8, token 8t + 2j+1)
+        float* const mine = red + warp * (kTok * kPitch);
 #pragma unroll
-        for (int s = 0; s < P; ++s) {
-            mine[(2 * j) * kPitch + s * 16 + g] = acc[s][0];
-            mine[(2 * j + 1) * kPitch + s * 16 + g] = acc[s][1];
-            mine[(2 * j) * kPitch + s * 16 + g + 8] = acc[s][2];
-            mine[(2 * j + 1) * kPitch + s * 16 + g + 8] = acc[s][3];
-        }
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int s = 0; s < P; ++s) {
+                mine[(8 * t + 2 * j) * kPitch + s * 16 + g] = acc[t][s][0];
+                mine[(8 * t + 2 * j + 1) * kPitch + s * 16 + g] = acc[t][s][1];
+                mine[(8 * t + 2 * j) * kPitch + s * 16 + g + 8] = acc[t][s][2];
+                mine[(8 * t + 2 * j + 1) * kPitch + s * 16 + g + 8] = acc[t][s][3];
+            }
         __syncthreads();
         auto sum_of = [&](int tok, int col) {
             float sum = 0.0f;
 #pragma unroll
-            for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (8 * kPitch) + tok * kPitch + col];
+            for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (kTok * kPitch) + tok * kPitch + col];
             return sum;
         };
         auto emit = [&](int tok, int col, float sum) {
@@ -316,10 +330,10 @@ small_m8_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, c
             }
         };
         if (sp.ks == 1) {
-            for (int o = threadIdx.x; o < 8 * kCols; o += kSmThreads) emit(o / kCols, o % kCols, sum_of(o / kCols, o % kCols));
+            for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) emit(o / kCols, o % kCols, sum_of(o / kCols, o % kCols));
             __syncthreads();
         } else {
-            split_finish<8, kCols>(sp, group, slice, &last_flag, sum_of, emit);
+            split_finish<kTok, kCols>(sp, group, slice, &last_flag, sum_of, emit);
         }
     }
 }
@@ -375,11 +389,11 @@ static cudaError_t launch_stream(Kernel kernel, int smem_bytes, int cols_per_ite
                               reinterpret_cast<uint16_t*>(L.c), L.M, L.N, L.K, L.ldc, L.out_mode, items, sp);
 }
 
-template <int P, int U>
+template <int P, int U, int NT = 1>
 static cudaError_t launch_small8(const StreamLaunch& L) {
     static std::mutex mu;
     static bool configured[64];
-    return launch_stream(small_m8_kernel<P, U>, kSmWarps * 8 * (P * 16 + 1) * static_cast<int>(sizeof(float)), P * 16, 8, L, configured, mu);
+    return launch_stream(small_m8_kernel<P, U, NT>, kSmWarps * 8 * NT * (P * 16 + 1) * static_cast<int>(sizeof(float)), P * 16, 8 * NT, L, configured, mu);
 }
 
 template <int MT, int P, int U>
@@ -396,7 +410,8 @@ static cudaError_t launch_small(const StreamLaunch& L) {
 struct StreamPlan {
     int p, ks;
 };
-static StreamPlan plan_stream(int N, int K, int sms, const int* p_choices, int n_choices, int strip_cols, int tokens, size_t ws_bytes) {
+static StreamPlan plan_stream(int N, int K, int sms, const int* p_choices, int n_choices, int strip_cols, int tokens, size_t ws_bytes,
+                              double split_cost = 40.0) {
     const int strips = (N + strip_cols - 1) / strip_cols;
     const int nkb = K / 16;
     StreamPlan best{1, 1};
@@ -412,7 +427,7 @@ static StreamPlan plan_stream(int N, int K, int sms, const int* p_choices, int n
             }
             const long long ctas = static_cast<long long>(groups) * ks;
             const long long rounds = (ctas + sms - 1) / sms;
-            const double per_cta = static_cast<double>(p) * nkb / ks + 60.0 + (ks > 1 ? 40.0 : 0.0);
+            const double per_cta = static_cast<double>(p) * nkb / ks + 60.0 + (ks > 1 ? split_cost : 0.0);
             const double cost = rounds * per_cta;
             if (best_cost < 0 || cost < best_cost * 0.98) {
                 best_cost = cost;
@@ -460,21 +475,19 @@ int small_m_launch(const void* a, const uint8_t* w, const float* scale, const vo
             default: break;
         }
     } else if (M <= 16) {
-        static const int kP[] = {16, 12, 10, 9, 8, 6, 5, 4, 3, 2, 1};
-        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 11, 8, 16, ws);
+        // Two groups of eight tokens against the same weight fragments.  With 16 tokens the trip through the workspace (fence,
+        // counter, the last CTA's reads) costs about as much as 700 k16-block-strips of streaming - measured 2.6 us against
+        // 3.7 ns per strip - so K is split only where that buys many more busy SMs.
+        static const int kP[] = {6, 5, 4, 3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 6, 16, 16, ws, 700.0);
         L.ks = pl.ks;
         switch (pl.p) {
-            FEATHER_SMALL_CASE(1, 16, 1)
-            FEATHER_SMALL_CASE(1, 12, 2)
-            FEATHER_SMALL_CASE(1, 10, 2)
-            FEATHER_SMALL_CASE(1, 9, 2)
-            FEATHER_SMALL_CASE(1, 8, 2)
-            FEATHER_SMALL_CASE(1, 6, 4)
-            FEATHER_SMALL_CASE(1, 5, 4)
-            FEATHER_SMALL_CASE(1, 4, 4)
-            FEATHER_SMALL_CASE(1, 3, 4)
-            FEATHER_SMALL_CASE(1, 2, 8)
-            FEATHER_SMALL_CASE(1, 1, 8)
+            case 6: e = launch_small8<6, 1, 2>(L); break;
+            case 5: e = launch_small8<5, 2, 2>(L); break;
+            case 4: e = launch_small8<4, 2, 2>(L); break;
+            case 3: e = launch_small8<3, 2, 2>(L); break;
+            case 2: e = launch_small8<2, 4, 2>(L); break;
+            case 1: e = launch_small8<1, 8, 2>(L); break;
             default: break;
         }
     } else {   // two token tiles: twice the accumulators, so at most 8 strips per item
