@@ -1271,13 +1271,18 @@ struct Types {
     int64_t lora_rank = 0;
 };
 
-// Bandwidth-bound end (at most 16 tokens, or on request): the register-streaming kernel, unless the caller pinned a
-// tensor-memory variant or the output goes to several buffers.  split_k = 1 only says "no workspace" (the reference-ABI
-// launcher passes it): the streaming kernel never splits K through a workspace either, so that alone pins nothing.
-static bool takes_streaming_kernel(const feather_mm_variant* variant, int64_t M, int n_extra) {
+// Bandwidth-bound end: the register-streaming kernel, unless the caller pinned a tensor-memory variant or the output goes to
+// several buffers.  Up to 16 tokens always; up to 24 tokens for weights of at most 32 MB, where the tensor-memory kernel's
+// fixed cost (pipeline fill and drain, about 7 us) weighs more than the streaming kernel's extra MMAs (measured at 17-24 tokens:
+// 11.7 against 15.3 us for 5120 x 5120, 10.9 against 14.5 us for 3072 x 9216, but 23.3 against 21.7 us for 5120 x 13824);
+// up to 32 tokens on request.  split_k = 1 only says "no workspace" (the reference-ABI launcher passes it): the streaming
+// kernel never needs a workspace to be correct, so that alone pins nothing.
+static bool takes_streaming_kernel(const feather_mm_variant* variant, int64_t M, int64_t N, int64_t K, int n_extra) {
     const int which = variant ? variant->kernel : FEATHER_KERNEL_AUTO;
     const bool pinned = variant && (variant->tokens_tile || variant->cta_pair || variant->split_k > 1 || variant->transform_groups);
-    return (which == FEATHER_KERNEL_STREAM || (which == FEATHER_KERNEL_AUTO && !pinned && M <= 16)) && n_extra == 0 && M <= 32;
+    const bool small_weight = N * K <= (int64_t(32) << 20);
+    const bool by_choice = which == FEATHER_KERNEL_AUTO && !pinned && (M <= 16 || (M <= 24 && small_weight));
+    return (which == FEATHER_KERNEL_STREAM || by_choice) && n_extra == 0 && M <= 32;
 }
 
 static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, const void* bias, void* c, int64_t M, int64_t N,
@@ -1322,7 +1327,7 @@ static int scaled_mm_impl(const void* a, const uint8_t* b, const float* scale, c
         if (n_extra != 0 || scatter_rows != 0) return set_error(FEATHER_ERR_UNSUPPORTED, "the LoRA term is not combined with sharded outputs");
     }
     const bool plain_operands = !types.a_bf16 && !types.w_e4m3 && !lora;
-    if (plain_operands && takes_streaming_kernel(variant, M, n_extra))
+    if (plain_operands && takes_streaming_kernel(variant, M, N, K, n_extra))
         return small_m_launch(a, b, scale, bias, c, M, N, K, ldc, output_dtype, flip_final, sms, workspace, workspace_bytes, stream);
     if (which == FEATHER_KERNEL_STREAM)
         return set_error(FEATHER_ERR_UNSUPPORTED, "the streaming kernel writes one output buffer and takes fp16 activations and e5m2 weights");
@@ -1597,7 +1602,7 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
     if (M == 0) return FEATHER_OK;
     // The register-streaming kernel splits K across CTAs through the scratch when the weight's columns alone cannot fill the
     // SMs; it gets the built-in array like the tensor-memory kernel below, with the counter block cleared first.
-    if (takes_streaming_kernel(variant, M, 0)) {
+    if (takes_streaming_kernel(variant, M, N, K, 0)) {
         void* scratch = nullptr;
         if (int st = static_scratch_of_current_device(&scratch)) return st;
         const cudaError_t e = cudaMemsetAsync(scratch, 0, kCounterBytes, stream);
@@ -1631,7 +1636,7 @@ extern "C" int feather_scaled_mm_static(const void* a, const uint8_t* b_prepacke
 extern "C" size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K, const feather_mm_variant* variant) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     int sms = sm_count_of_current_device();
-    if (takes_streaming_kernel(variant, M, 0)) return small_m_workspace_bytes(M, N, K, sms);
+    if (takes_streaming_kernel(variant, M, N, K, 0)) return small_m_workspace_bytes(M, N, K, sms);
     Plan pl;
     if (!make_plan(M, N, K, variant, 0, false, sms, &pl)) return 0;
     return pl.ws_bytes;
@@ -1647,7 +1652,7 @@ extern "C" int feather_scaled_mm_choose(int64_t M, int64_t N, int64_t K, size_t 
     out->split_k = pl.splits;
     out->transform_groups = pl.tg;
     out->max_ctas = 0;
-    out->kernel = M <= 16 ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
+    out->kernel = takes_streaming_kernel(nullptr, M, N, K, 0) ? FEATHER_KERNEL_STREAM : FEATHER_KERNEL_TMEM;
     out->staging = 0;
     return FEATHER_OK;
 }

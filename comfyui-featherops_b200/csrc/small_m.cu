@@ -6,11 +6,10 @@
 //
 //   work item   P strips of output columns n, all of K; P is picked so the items fill the SMs in as few, as full rounds as possible
 //   CTA         16 warps; warp w takes the k16-blocks [w*KB/16, (w+1)*KB/16) of the item, so the K split needs no workspace
-//   up to 16 tokens (small_m8_kernel): a strip is 16 columns; per k16-block and strip two 32-bit loads per lane straight from
-//               the prepacked layout (a warp load is 128 contiguous bytes), 4 x prmt (e5m2 -> fp16 is byte << 8) build the
-//               16 n x 16 k MMA operand once, and one mma.sync.m16n8k16 per group of eight tokens multiplies it (fp32
-//               accumulate); token fragments come from global/L1 and are reused across the P strips
-//   17..32 tokens, on request (small_m_kernel): a strip is 8 columns, the tokens are the 16-row operand, two tiles of them
+//   per k16-block and strip of 16 columns: two 32-bit loads per lane straight from the prepacked layout (a warp load is 128
+//               contiguous bytes), 4 x prmt (e5m2 -> fp16 is byte << 8) build the 16 n x 16 k MMA operand once, and one
+//               mma.sync.m16n8k16 per group of eight tokens multiplies it (fp32 accumulate); token fragments come from
+//               global/L1 and are reused across the P strips.  One to four token groups (up to 32 tokens).
 //   reduce      the 16 warps' fp32 partials go through shared memory and are added in warp order (deterministic), then
 //               * scale -> RTNE -> + bias in the output dtype, as in the tensor-memory kernel
 //
@@ -92,136 +91,11 @@ __device__ __forceinline__ uint16_t sm_finish(float acc, float scale, int out_mo
     return __half_as_ushort(v);
 }
 
-// MT: 16-token tiles (instantiated for 2: 17..32 tokens; up to 16 tokens take small_m8_kernel below, which builds each weight
-// fragment once for both groups of eight tokens and measured 5-14 % faster); P: strips of 8 n per work item; U: k16-blocks
-// whose loads are issued together.
-//
 // Inside a k16-block the MMA's k index is permuted (the sum over k does not care): MMA k = 2j, 2j+1 is physical
 // k = 4j, 4j+1 and MMA k = 2j+8, 2j+9 is physical k = 4j+2, 4j+3.  Lane (g, j) then needs exactly the aligned 32-bit word j
-// of chunk g - a warp load is 128 contiguous bytes - and one 64-bit token load per row.
-template <int MT, int P, int U>
-__global__ void __launch_bounds__(kSmThreads, 1)
-small_m_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ w, const float* __restrict__ scale_ptr,
-               const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, long long ldc, int out_bf16, int num_items,
-               SplitArgs sp) {
-    constexpr int kTok = MT * 16;
-    constexpr int kCols = P * 8;
-    constexpr int kPitch = kCols + 1;
-    extern __shared__ float red[];                          // [kSmWarps][kTok][kPitch]
-    __shared__ int last_flag;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, j = lane & 3;
-    const int nkb = K / 16;
-    pdl_launch_dependents();
-    pdl_wait_for_previous_kernel();
-    const float scale = scale_ptr != nullptr ? __ldg(scale_ptr) : 1.0f;
-    const bool has_bias = bias != nullptr;
-
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-        // item = (group of P strips, K slice); the slice's k16-blocks are split over the 16 warps
-        const int group = item / sp.ks, slice = item - group * sp.ks;
-        const int sl_begin = static_cast<int>(static_cast<long long>(slice) * nkb / sp.ks);
-        const int sl_end = static_cast<int>(static_cast<long long>(slice + 1) * nkb / sp.ks);
-        const int kb_begin = sl_begin + static_cast<int>(static_cast<long long>(warp) * (sl_end - sl_begin) / kSmWarps);
-        const int kb_end = sl_begin + static_cast<int>(static_cast<long long>(warp + 1) * (sl_end - sl_begin) / kSmWarps);
-        const int n_base = group * kCols;
-        float acc[MT][P][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int s = 0; s < P; ++s)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[mt][s][i] = 0.0f;
-
-        // this lane's word in the first k16-block plane, strip 0; strips are 128 bytes apart, planes N*16 bytes apart
-        const uint8_t* const w_lane = w + static_cast<long long>(n_base) * 16 + lane * 4;
-        const long long plane = static_cast<long long>(N) * 16;
-
-        // Two register buffers: the loads of the next U k16-blocks are issued before the current block is multiplied, so the
-        // warp always has a block of loads in flight (a plain load-then-compute loop drains the memory pipeline every turn).
-        auto load_block = [&](int kb0, uint32_t (&wv)[U][P], uint2 (&af)[U][MT][2]) {
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int kb = kb0 + u;
-                const bool kb_ok = kb < kb_end;
-#pragma unroll
-                for (int s = 0; s < P; ++s) {
-                    wv[u][s] = 0u;
-                    if (kb_ok && n_base + s * 8 + g < N) wv[u][s] = __ldg(reinterpret_cast<const uint32_t*>(w_lane + kb * plane + s * 128));
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int r0 = mt * 16 + g, r1 = r0 + 8;
-                    const long long k = static_cast<long long>(kb) * 16 + 4 * j;
-                    af[u][mt][0] = (kb_ok && r0 < M) ? __ldg(reinterpret_cast<const uint2*>(a + r0 * static_cast<long long>(K) + k)) : make_uint2(0u, 0u);
-                    af[u][mt][1] = (kb_ok && r1 < M) ? __ldg(reinterpret_cast<const uint2*>(a + r1 * static_cast<long long>(K) + k)) : make_uint2(0u, 0u);
-                }
-            }
-        };
-        auto multiply_block = [&](const uint32_t (&wv)[U][P], const uint2 (&af)[U][MT][2]) {
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int s = 0; s < P; ++s) {
-                    const uint32_t b0 = __byte_perm(wv[u][s], 0u, 0x1404);     // physical k = 4j, 4j+1   -> fp16 pair (byte << 8)
-                    const uint32_t b1 = __byte_perm(wv[u][s], 0u, 0x3424);     // physical k = 4j+2, 4j+3
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint32_t frag[4] = {af[u][mt][0].x, af[u][mt][1].x, af[u][mt][0].y, af[u][mt][1].y};
-                        mma_m16n8k16(acc[mt][s], frag, b0, b1);
-                    }
-                }
-        };
-        uint32_t w0[U][P], w1[U][P];
-        uint2 a0[U][MT][2], a1[U][MT][2];
-        int kb0 = kb_begin;
-        if (kb0 < kb_end) load_block(kb0, w0, a0);
-        while (kb0 < kb_end) {
-            const int kb1 = kb0 + U;
-            if (kb1 < kb_end) load_block(kb1, w1, a1);
-            multiply_block(w0, a0);
-            if (kb1 >= kb_end) break;
-            kb0 = kb1 + U;
-            if (kb0 < kb_end) load_block(kb0, w0, a0);
-            multiply_block(w1, a1);
-        }
-
-        // fragment layout of D: d0 (row g, col 2j), d1 (row g, col 2j+1), d2 (row g+8, col 2j), d3 (row g+8, col 2j+1)
-        float* const mine = red + warp * (kTok * kPitch);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int s = 0; s < P; ++s) {
-                mine[(mt * 16 + g) * kPitch + s * 8 + 2 * j] = acc[mt][s][0];
-                mine[(mt * 16 + g) * kPitch + s * 8 + 2 * j + 1] = acc[mt][s][1];
-                mine[(mt * 16 + g + 8) * kPitch + s * 8 + 2 * j] = acc[mt][s][2];
-                mine[(mt * 16 + g + 8) * kPitch + s * 8 + 2 * j + 1] = acc[mt][s][3];
-            }
-        __syncthreads();
-        auto sum_of = [&](int tok, int col) {
-            float sum = 0.0f;
-#pragma unroll
-            for (int wi = 0; wi < kSmWarps; ++wi) sum += red[wi * (kTok * kPitch) + tok * kPitch + col];   // warp order: deterministic
-            return sum;
-        };
-        auto emit = [&](int tok, int col, float sum) {
-            const int n = n_base + col;
-            if (tok < M && n < N) {
-                const uint16_t bias_bits = has_bias ? __ldg(bias + n) : uint16_t(0);
-                c[static_cast<long long>(tok) * ldc + n] = sm_finish(sum, scale, out_bf16, has_bias, bias_bits);
-            }
-        };
-        if (sp.ks == 1) {
-            for (int o = threadIdx.x; o < kTok * kCols; o += kSmThreads) emit(o / kCols, o % kCols, sum_of(o / kCols, o % kCols));
-            __syncthreads();
-        } else {
-            split_finish<kTok, kCols>(sp, group, slice, &last_flag, sum_of, emit);
-        }
-    }
-}
-
-// Up to 8 * NT tokens (NT = 1 or 2): the weights are the 16-row MMA operand (16 n x 16 k = 256 bytes of weights per MMA and
+// of a 16-byte chunk - a warp load is 128 contiguous bytes - and one 64-bit token load per row.
+//
+// Up to 8 * NT tokens (NT = 1 .. 4): the weights are the 16-row MMA operand (16 n x 16 k = 256 bytes of weights per MMA and
 // token group) and each group of eight tokens the 8-column operand; the weight fragment of a strip is built once and
 // multiplied with every token group.  P: strips of 16 n per item.
 template <int P, int U, int NT>
@@ -396,13 +270,6 @@ static cudaError_t launch_small8(const StreamLaunch& L) {
     return launch_stream(small_m8_kernel<P, U, NT>, kSmWarps * 8 * NT * (P * 16 + 1) * static_cast<int>(sizeof(float)), P * 16, 8 * NT, L, configured, mu);
 }
 
-template <int MT, int P, int U>
-static cudaError_t launch_small(const StreamLaunch& L) {
-    static std::mutex mu;
-    static bool configured[64];
-    return launch_stream(small_m_kernel<MT, P, U>, kSmWarps * MT * 16 * (P * 8 + 1) * static_cast<int>(sizeof(float)), P * 8, MT * 16, L, configured, mu);
-}
-
 // How the weight is cut into CTA-sized pieces: P strips per work item (token fragments are reused across the strips of an
 // item) and ks K slices per item.  Cost model: rounds of CTAs over the SMs x k16-block-strips per CTA, plus a fixed
 // per-CTA cost (prologue, in-CTA reduction, and for a split the trip through the workspace) counted in the same unit.
@@ -438,8 +305,6 @@ static StreamPlan plan_stream(int N, int K, int sms, const int* p_choices, int n
     return best;
 }
 
-#define FEATHER_SMALL_CASE(MT_, P_, U_) \
-    case P_: e = launch_small<MT_, P_, U_>(L); break;
 #define FEATHER_SMALL8_CASE(P_, U_) \
     case P_: e = launch_small8<P_, U_>(L); break;
 
@@ -490,18 +355,25 @@ int small_m_launch(const void* a, const uint8_t* w, const float* scale, const vo
             case 1: e = launch_small8<1, 8, 2>(L); break;
             default: break;
         }
-    } else {   // two token tiles: twice the accumulators, so at most 8 strips per item
-        static const int kP[] = {8, 6, 5, 4, 3, 2, 1};
-        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 7, 8, 32, ws);
+    } else if (M <= 24) {   // three groups of eight tokens
+        static const int kP[] = {4, 3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 4, 16, 24, ws, 900.0);
         L.ks = pl.ks;
         switch (pl.p) {
-            FEATHER_SMALL_CASE(2, 8, 1)
-            FEATHER_SMALL_CASE(2, 6, 1)
-            FEATHER_SMALL_CASE(2, 5, 2)
-            FEATHER_SMALL_CASE(2, 4, 2)
-            FEATHER_SMALL_CASE(2, 3, 2)
-            FEATHER_SMALL_CASE(2, 2, 4)
-            FEATHER_SMALL_CASE(2, 1, 4)
+            case 4: e = launch_small8<4, 1, 3>(L); break;
+            case 3: e = launch_small8<3, 2, 3>(L); break;
+            case 2: e = launch_small8<2, 2, 3>(L); break;
+            case 1: e = launch_small8<1, 4, 3>(L); break;
+            default: break;
+        }
+    } else {                // four groups
+        static const int kP[] = {3, 2, 1};
+        const StreamPlan pl = plan_stream(L.N, L.K, sms, kP, 3, 16, 32, ws, 1100.0);
+        L.ks = pl.ks;
+        switch (pl.p) {
+            case 3: e = launch_small8<3, 1, 4>(L); break;
+            case 2: e = launch_small8<2, 2, 4>(L); break;
+            case 1: e = launch_small8<1, 4, 4>(L); break;
             default: break;
         }
     }

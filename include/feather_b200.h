@@ -58,7 +58,7 @@ enum { FEATHER_SRC_FP32 = 0, FEATHER_SRC_BF16 = 1, FEATHER_SRC_FP16 = 2 };
  *   split_k     : number of K slices reduced through the fp32 workspace (1 = none)
  *   transform_groups : groups of four warps that upcast e5m2 weight stages (1 or 2)
  *   max_ctas    : cap on the persistent grid (0 = number of SMs)
- *   kernel      : 0 = choose from the shape (streaming up to 16 tokens); 1 = the tensor-memory (tcgen05) kernel; 2 = the
+ *   kernel      : 0 = choose from the shape (streaming up to 16 tokens, up to 24 for weights of at most 32 MB); 1 = the tensor-memory (tcgen05) kernel; 2 = the
  *                 register-streaming kernel, at most 32 tokens (needs no workspace, ignores the other fields)
  *   staging     : output staging of 256-token pair tiles: 0 = choose (two buffers per epilogue group when blocks also go to
  *                 peer GPUs, one otherwise), 1 = one buffer, 2 = two buffers
@@ -82,8 +82,8 @@ typedef struct feather_mm_variant {
  * order and meaning, cudaStream_t in place of hipStream_t.  The five tile integers are accepted and
  * ignored (the variant is chosen from the shape); b_dtype is 1 (e5m2) or 0 (e4m3fn, upcast exactly).  Returns 1 when the launch
  * was enqueued, 0 otherwise (the reference returns false for an unknown config).  This entry point
- * takes no workspace, so it never splits K through one: up to 16 tokens it runs the register-streaming kernel (which
- * splits K inside a CTA), above that the tensor-memory kernel unsplit. */
+ * takes no workspace, so it never splits K through one: where the shape calls for it (up to 16 tokens, up to 24 for small
+ * weights) it runs the register-streaming kernel (which splits K inside a CTA), else the tensor-memory kernel unsplit. */
 FEATHER_API int launch_scaled_mm(const void* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
                      int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, int block_warps_m, int block_warps_n,
                      int unroll_k, int repeat_m, int repeat_n, int b_dtype, int output_dtype, feather_stream_t stream);
@@ -116,7 +116,7 @@ FEATHER_API int feather_scaled_mm_ex(const void* a, const uint8_t* b_prepacked, 
  *   output_dtype dtype the scaled sum is rounded to and the bias is added in (bias has this dtype), as in feather_scaled_mm_ex
  *   final_dtype  dtype of c: -1 or output_dtype stores that value; the other 16-bit dtype applies one more rounding first,
  *                which is the caller's `y.to(dtype_orig)` (comfy_feather/ops.py:103) done in the epilogue.
- * Everything else as feather_scaled_mm_ex.  Up to 16 tokens of fp16 activations with e5m2 weights take the streaming kernel as
+ * Everything else as feather_scaled_mm_ex.  A handful of tokens of fp16 activations with e5m2 weights take the streaming kernel as
  * there; bf16 activations and e4m3 weights always take the tensor-memory kernel. */
 FEATHER_API int feather_scaled_mm_typed(const void* a, int a_dtype, const uint8_t* b_prepacked, int b_dtype, const float* scale, const void* bias,
                                         void* c, int64_t M, int64_t N, int64_t K, int64_t ldc, int output_dtype, int final_dtype,
@@ -202,7 +202,7 @@ FEATHER_API size_t feather_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64
  *   - A K split the library chooses itself (variant NULL or split_k 0) is shrunk to what the array holds, exactly as
  *     feather_scaled_mm_ex shrinks it to the caller's workspace.  Only a variant that pins a larger split_k is rejected,
  *     with FEATHER_ERR_WORKSPACE (the message says how much is needed): pass a smaller split_k, or use feather_scaled_mm_ex.
- *   - Up to 16 tokens the library's own choice is the register-streaming kernel; it uses the array only for the counters
+ *   - For a handful of tokens the library's own choice is the register-streaming kernel; it uses the array only for the counters
  *     and partial sums of a K split across CTAs, which it chooses when the weight's columns alone cannot fill the SMs.
  *   - The call allocates and frees nothing.  The first call on each device that needs the array looks its device address
  *     up (cudaGetSymbolAddress, with that device current) and keeps it; make that first call outside any stream capture.
