@@ -185,7 +185,7 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
 // Optional cycle accounting (MmParams::stats): each role of CTA 0 sums the SM cycles it spends in each of its waits.
 // slots: 0 token producer total, 1 its wait for a free stage, 2/3 the same for the weight producer | 4 mma total, 5 mma wait acc-free, 6 mma wait tokens, 7 mma wait weights
 //        8 transform(warp 0 of group 0) total, 9 wait weight bytes, 10 wait tmem-free | 12 epilogue(warp 0) total, 13 wait acc-full,
-//        14 inside store chunks, 15 chunks
+//        14 inside store chunks, 15 chunks, 11 from accumulator-full seen to accumulator handed back
 struct StatTimer {
     long long t0;
     bool on;
@@ -692,6 +692,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         uint16_t* const c16 = reinterpret_cast<uint16_t*>(p.c);
         constexpr int kTileCols = kBW * CG;
         constexpr int kOutRows = C::kOutRows;
+        constexpr bool kHoldTile = TN == 256 && TG == 1 && kAccs == 1;
         const bool staged = p.tma_store != 0 && p.splits == 1;
         const uint32_t out_base = smem_out + grp * (C::kOutBufs * C::kOutBufBytes);
         uint32_t ui = 0;
@@ -701,7 +702,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         bool alive = true;
         const bool stat = p.stats != nullptr && blockIdx.x == 0 && warp == 0;
         StatTimer tt(stat), tw(stat);
-        long long st_total = 0, st_full = 0, st_emit = 0, st_chunks = 0;
+        long long st_total = 0, st_full = 0, st_emit = 0, st_chunks = 0, st_release = 0, t_full = 0;
         tt.start();
         for (int u = cluster_id; u < p.num_units; u += num_clusters, ++ui) {
             const Unit w = decode_unit<TN, CG>(p, u);
@@ -711,6 +712,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 tw.start();
                 const bool got = mbar_wait_warp(bar_accfull + 8 * a, aph, abort_flag, lane);
                 tw.stop(st_full);
+                if (stat) t_full = clock64();
                 if (!got) {
                     if (lane == 0) give_up<CG>(p, abort_flag, kRoleEpilogue, warp);
                     alive = false;
@@ -745,6 +747,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             auto release_acc = [&]() {
                 if (released) return;
                 released = true;
+                if (stat) st_release += clock64() - t_full;
                 if (!alive) return;
                 tc_fence_before();
                 __syncwarp();
@@ -779,6 +782,138 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 // thread t supplies the address of row t % 8 of matrix t / 8
                 const uint32_t st_lane = (q >> 1) * (kOutRows * 128) + (lane & 7) * 128 +
                                          (((static_cast<uint32_t>(q & 1) * 4 + (lane >> 3)) ^ (lane & 7)) << 4);
+                auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+                    tmem_ld_16x256b_x2(frag + c, lo);
+                    tmem_ld_16x256b_x2(frag_hi + c, hi);
+                };
+                auto add_second = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {   // the odd k-blocks' partial sum
+                    uint32_t lo2[8], hi2[8];
+                    tmem_ld_16x256b_x2(frag + TN + c, lo2);
+                    tmem_ld_16x256b_x2(frag_hi + TN + c, hi2);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(lo2[j]));
+                        hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(hi2[j]));
+                    }
+                };
+                // One bulk group per block: with two buffers the group before the last may still be reading.
+                auto block_begin = [&]() {
+                    if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                };
+                auto block_end = [&](uint32_t buf, int c0) {
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                    if (group_leader) {
+                        // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
+                        int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
+                        if (EXT && p.scatter_rows > 0 && d_end > 0) {
+                            // row-sharded destinations: the block goes to the one buffer that owns its token rows
+                            d_begin = row / p.scatter_rows;
+                            row -= d_begin * p.scatter_rows;
+                            d_end = d_begin + 1;
+                        }
+                        for (int d = d_begin; d < d_end; ++d) {
+                            if (p.c3d) {
+                                tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
+                            } else {
+                                tma_store_2d(&tmap_c.m[d], buf, store_x, row);
+                                if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
+                            }
+                        }
+                        tma_store_commit();
+                    }
+                };
+                // 256-token tiles with one transform group (the long-GEMM variant; 480 threads leave 128 registers each): the first of
+                // the group's four blocks goes through the staging buffer at once (nothing has used the buffer since the previous
+                // tile), the other three are read, scaled, rounded and packed into 48 registers; then the accumulator goes back
+                // to the MMA warps, and only then are the parked blocks staged and stored.  The tensor cores so wait for the
+                // tensor-memory loads alone, not for the staging buffer's round trips through the store engine.  Output type,
+                // bias and final cast are run-time (warp-uniform) branches here: one copy of this code keeps the values in
+                // registers, eight copies made the compiler park them in local memory.
+                auto drain_held = [&]() {
+                    auto pack = [&](uint32_t x0, uint32_t x1, uint32_t b2) -> uint32_t {
+                        const float r0 = __uint_as_float(x0) * scale, r1 = __uint_as_float(x1) * scale;
+                        if (out_bf16) {
+                            __nv_bfloat162 x = __floats2bfloat162_rn(r0, r1);
+                            if (has_bias) x = __hadd2(x, *reinterpret_cast<const __nv_bfloat162*>(&b2));
+                            if (flip) {
+                                const float2 f = __bfloat1622float2(x);
+                                const __half2 y = __floats2half2_rn(f.x, f.y);
+                                return *reinterpret_cast<const uint32_t*>(&y);
+                            }
+                            return *reinterpret_cast<const uint32_t*>(&x);
+                        } else {
+                            __half2 x = __floats2half2_rn(r0, r1);
+                            if (has_bias) x = __hadd2(x, *reinterpret_cast<const __half2*>(&b2));
+                            if (flip) {
+                                const float2 f = __half22float2(x);
+                                const __nv_bfloat162 y = __floats2bfloat162_rn(f.x, f.y);
+                                return *reinterpret_cast<const uint32_t*>(&y);
+                            }
+                            return *reinterpret_cast<const uint32_t*>(&x);
+                        }
+                    };
+                    auto pack16 = [&](const uint32_t (&lo)[8], const uint32_t (&hi)[8], uint32_t (&dst)[16], auto half_tag) {
+                        constexpr int kAt = decltype(half_tag)::value * 8;
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            dst[kAt + 4 * g + 0] = pack(lo[4 * g], lo[4 * g + 1], bias2[0]);
+                            dst[kAt + 4 * g + 1] = pack(lo[4 * g + 2], lo[4 * g + 3], bias2[1]);
+                            dst[kAt + 4 * g + 2] = pack(hi[4 * g], hi[4 * g + 1], bias2[2]);
+                            dst[kAt + 4 * g + 3] = pack(hi[4 * g + 2], hi[4 * g + 3], bias2[3]);
+                        }
+                    };
+                    auto stage = [&](const uint32_t (&v)[16], uint32_t buf) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) stmatrix_x4_trans(buf + st_lane + (8 * g) * 128, v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                    };
+                    constexpr int kBlocks = TN / (2 * kOutRows);
+                    constexpr int kHeld = kBlocks > 1 ? kBlocks - 1 : 1;          // (only instantiated meaningfully for 256-token tiles)
+                    uint32_t held[kHeld][16];
+                    {
+                        // Blocks 1.. of the group are parked first, then block 0 is read; the accumulator goes back as soon as block 0's
+                        // last load has landed, before anything is staged.
+                        uint32_t lo[8], hi[8], now[16];
+#pragma unroll
+                        for (int b = 0; b < kHeld; ++b) {
+                            const int c0 = first + (b + 1) * 2 * kOutRows;
+                            if (c0 < valid) {
+                                load16(c0, lo, hi);
+                                tc_wait_ld();
+                                pack16(lo, hi, held[b], std::integral_constant<int, 0>{});
+                                load16(c0 + 16, lo, hi);
+                                tc_wait_ld();
+                                pack16(lo, hi, held[b], std::integral_constant<int, 1>{});
+                            }
+                        }
+                        if (first < valid) {
+                            const uint32_t buf = out_base + (out_flip % C::kOutBufs) * C::kOutBufBytes;
+                            load16(first, lo, hi);
+                            tc_wait_ld();
+                            pack16(lo, hi, now, std::integral_constant<int, 0>{});
+                            load16(first + 16, lo, hi);
+                            tc_wait_ld();
+                            release_acc();
+                            pack16(lo, hi, now, std::integral_constant<int, 1>{});
+                            block_begin();
+                            stage(now, buf);
+                            block_end(buf, first);
+                        }
+                    }
+                    release_acc();
+#pragma unroll
+                    for (int b = 0; b < kHeld; ++b) {
+                        const int c0 = first + (b + 1) * 2 * kOutRows;
+                        if (c0 < valid) {
+                            const uint32_t buf = out_base + ((out_flip + static_cast<uint32_t>(b + 1)) % C::kOutBufs) * C::kOutBufBytes;
+                            block_begin();
+                            stage(held[b], buf);
+                            block_end(buf, c0);
+                        }
+                    }
+                };
                 auto drain = [&](auto bf16_tag, auto bias_tag, auto flip_tag) {
                     constexpr bool kBf16 = decltype(bf16_tag)::value;
                     constexpr bool kBias = decltype(bias_tag)::value;
@@ -811,49 +946,6 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         for (int g = 0; g < 2; ++g)
                             stmatrix_x4_trans(buf + st_lane + (row0 + 8 * g) * 128, pack(lo[4 * g], lo[4 * g + 1], bias2[0]), pack(lo[4 * g + 2], lo[4 * g + 3], bias2[1]),
                                               pack(hi[4 * g], hi[4 * g + 1], bias2[2]), pack(hi[4 * g + 2], hi[4 * g + 3], bias2[3]));
-                    };
-                    auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
-                        tmem_ld_16x256b_x2(frag + c, lo);
-                        tmem_ld_16x256b_x2(frag_hi + c, hi);
-                    };
-                    auto add_second = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {   // the odd k-blocks' partial sum
-                        uint32_t lo2[8], hi2[8];
-                        tmem_ld_16x256b_x2(frag + TN + c, lo2);
-                        tmem_ld_16x256b_x2(frag_hi + TN + c, hi2);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(lo2[j]));
-                            hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(hi2[j]));
-                        }
-                    };
-                    // One bulk group per block: with two buffers the group before the last may still be reading.
-                    auto block_begin = [&]() {
-                        if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
-                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                    };
-                    auto block_end = [&](uint32_t buf, int c0) {
-                        fence_proxy_async_smem();
-                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                        if (group_leader) {
-                            // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
-                            int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
-                            if (EXT && p.scatter_rows > 0 && d_end > 0) {
-                                // row-sharded destinations: the block goes to the one buffer that owns its token rows
-                                d_begin = row / p.scatter_rows;
-                                row -= d_begin * p.scatter_rows;
-                                d_end = d_begin + 1;
-                            }
-                            for (int d = d_begin; d < d_end; ++d) {
-                                if (p.c3d) {
-                                    tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
-                                } else {
-                                    tma_store_2d(&tmap_c.m[d], buf, store_x, row);
-                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
-                                }
-                            }
-                            tma_store_commit();
-                        }
                     };
                     constexpr int kPasses = kOutRows / 16;                         // 16 token rows per pass
                     if constexpr (kIssuers == 2) {
@@ -906,7 +998,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                 };
                 tw.start();
-                if (alive) {
+                if (alive && kHoldTile) {
+                    if constexpr (kHoldTile) drain_held();
+                } else if (alive) {
                     auto with_flip = [&](auto bf16_tag, auto bias_tag) {
                         if (flip) drain(bf16_tag, bias_tag, std::true_type{});
                         else drain(bf16_tag, bias_tag, std::false_type{});
@@ -1010,6 +1104,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             p.stats[13] = st_full;
             p.stats[14] = st_emit;
             p.stats[15] = st_chunks;
+            p.stats[11] = st_release;      // from accumulator-full seen to accumulator handed back
         }
         if (group_leader) tma_store_wait_all<0>();               // shared memory must outlive the stores that read it
     }
