@@ -185,7 +185,7 @@ __device__ __forceinline__ Unit decode_unit(const MmParams& p, int u) {
 // Optional cycle accounting (MmParams::stats): each role of CTA 0 sums the SM cycles it spends in each of its waits.
 // slots: 0 token producer total, 1 its wait for a free stage, 2/3 the same for the weight producer | 4 mma total, 5 mma wait acc-free, 6 mma wait tokens, 7 mma wait weights
 //        8 transform(warp 0 of group 0) total, 9 wait weight bytes, 10 wait tmem-free | 12 epilogue(warp 0) total, 13 wait acc-full,
-//        14 inside store chunks, 15 chunks, 11 from accumulator-full seen to accumulator handed back
+//        14 inside store chunks, 15 chunks
 struct StatTimer {
     long long t0;
     bool on;
@@ -702,28 +702,36 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         bool alive = true;
         const bool stat = p.stats != nullptr && blockIdx.x == 0 && warp == 0;
         StatTimer tt(stat), tw(stat);
-        long long st_total = 0, st_full = 0, st_emit = 0, st_chunks = 0, st_release = 0, t_full = 0;
+        long long st_total = 0, st_full = 0, st_emit = 0, st_chunks = 0;
         tt.start();
         for (int u = cluster_id; u < p.num_units; u += num_clusters, ++ui) {
             const Unit w = decode_unit<TN, CG>(p, u);
             const uint32_t a = ui % kAccs;
             const uint32_t aph = (ui / kAccs) & 1u;
+            // The tile's bias values are fetched before the wait for its accumulator, so their latency is not part of the read-back.
+            const int col_local = q * 32 + lane;                                  // column inside this CTA's 128
+            const int col = static_cast<int>(rank) * kBW + col_local;             // column inside the tile
+            const int n = w.n0 + col;
+            const bool n_ok = n < p.N;
+            const uint16_t bias_bits = (has_bias && n_ok) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + n) : uint16_t(0);
+            // the staged path's fragment layout: this thread's four output columns (one per matrix), bias duplicated into both halves of a word
+            uint32_t bias2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int nn = w.n0 + static_cast<int>(rank) * kBW + q * 32 + 8 * i + (lane >> 2);
+                const uint32_t bb = (has_bias && nn < p.N) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + nn) : 0u;
+                bias2[i] = bb * 0x00010001u;
+            }
             if (alive) {
                 tw.start();
                 const bool got = mbar_wait_warp(bar_accfull + 8 * a, aph, abort_flag, lane);
                 tw.stop(st_full);
-                if (stat) t_full = clock64();
                 if (!got) {
                     if (lane == 0) give_up<CG>(p, abort_flag, kRoleEpilogue, warp);
                     alive = false;
                 }
             }
             tc_fence_after();
-            const int col_local = q * 32 + lane;                                  // column inside this CTA's 128
-            const int col = static_cast<int>(rank) * kBW + col_local;             // column inside the tile
-            const int n = w.n0 + col;
-            const bool n_ok = n < p.N;
-            const uint16_t bias_bits = (has_bias && n_ok) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + n) : uint16_t(0);
             const uint32_t src = tmem_base + t_lane + a * (kIssuers * TN);
             // With two issuers the tile's sum is split over two accumulators (even / odd k-blocks); a tile of one k-block has
             // nothing in the second.
@@ -747,7 +755,6 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             auto release_acc = [&]() {
                 if (released) return;
                 released = true;
-                if (stat) st_release += clock64() - t_full;
                 if (!alive) return;
                 tc_fence_before();
                 __syncwarp();
@@ -771,68 +778,48 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 const int store_x = w.n0 + static_cast<int>(rank) * kBW;
                 const uint32_t frag = src;                                         // lanes q*32 .. +15; +16 lanes for the upper half
                 const uint32_t frag_hi = src + (16u << 16);
-                // this thread's four output columns (one per matrix) and their bias, duplicated into both halves of a word
-                uint32_t bias2[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int nn = w.n0 + static_cast<int>(rank) * kBW + q * 32 + 8 * i + (lane >> 2);
-                    const uint32_t bb = (has_bias && nn < p.N) ? __ldg(reinterpret_cast<const uint16_t*>(p.bias) + nn) : 0u;
-                    bias2[i] = bb * 0x00010001u;
-                }
                 // thread t supplies the address of row t % 8 of matrix t / 8
                 const uint32_t st_lane = (q >> 1) * (kOutRows * 128) + (lane & 7) * 128 +
                                          (((static_cast<uint32_t>(q & 1) * 4 + (lane >> 3)) ^ (lane & 7)) << 4);
-                auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
-                    tmem_ld_16x256b_x2(frag + c, lo);
-                    tmem_ld_16x256b_x2(frag_hi + c, hi);
-                };
-                auto add_second = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {   // the odd k-blocks' partial sum
-                    uint32_t lo2[8], hi2[8];
-                    tmem_ld_16x256b_x2(frag + TN + c, lo2);
-                    tmem_ld_16x256b_x2(frag_hi + TN + c, hi2);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(lo2[j]));
-                        hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(hi2[j]));
-                    }
-                };
-                // One bulk group per block: with two buffers the group before the last may still be reading.
-                auto block_begin = [&]() {
-                    if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
-                    asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                };
-                auto block_end = [&](uint32_t buf, int c0) {
-                    fence_proxy_async_smem();
-                    asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
-                    if (group_leader) {
-                        // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
-                        int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
-                        if (EXT && p.scatter_rows > 0 && d_end > 0) {
-                            // row-sharded destinations: the block goes to the one buffer that owns its token rows
-                            d_begin = row / p.scatter_rows;
-                            row -= d_begin * p.scatter_rows;
-                            d_end = d_begin + 1;
-                        }
-                        for (int d = d_begin; d < d_end; ++d) {
-                            if (p.c3d) {
-                                tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
-                            } else {
-                                tma_store_2d(&tmap_c.m[d], buf, store_x, row);
-                                if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
-                            }
-                        }
-                        tma_store_commit();
-                    }
-                };
-                // 256-token tiles with one transform group (the long-GEMM variant; 480 threads leave 128 registers each): the first of
-                // the group's four blocks goes through the staging buffer at once (nothing has used the buffer since the previous
-                // tile), the other three are read, scaled, rounded and packed into 48 registers; then the accumulator goes back
-                // to the MMA warps, and only then are the parked blocks staged and stored.  The tensor cores so wait for the
+                // 256-token tiles with one transform group (the long-GEMM variant; 480 threads leave 128 registers each): three of
+                // the group's four blocks are read, scaled, rounded and packed into 48 registers, then the fourth is read; the
+                // accumulator goes back to the MMA warps as soon as the last load has landed, and only then are the blocks staged
+                // and stored.  The tensor cores so wait for the
                 // tensor-memory loads alone, not for the staging buffer's round trips through the store engine.  Output type,
                 // bias and final cast are run-time (warp-uniform) branches here: one copy of this code keeps the values in
                 // registers, eight copies made the compiler park them in local memory.
                 auto drain_held = [&]() {
+                    auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+                        tmem_ld_16x256b_x2(frag + c, lo);
+                        tmem_ld_16x256b_x2(frag_hi + c, hi);
+                    };
+                    auto block_begin = [&]() {
+                        if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                    };
+                    auto block_end = [&](uint32_t buf, int c0) {
+                        fence_proxy_async_smem();
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                        if (group_leader) {
+                            // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
+                            int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
+                            if (EXT && p.scatter_rows > 0 && d_end > 0) {
+                                // row-sharded destinations: the block goes to the one buffer that owns its token rows
+                                d_begin = row / p.scatter_rows;
+                                row -= d_begin * p.scatter_rows;
+                                d_end = d_begin + 1;
+                            }
+                            for (int d = d_begin; d < d_end; ++d) {
+                                if (p.c3d) {
+                                    tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
+                                } else {
+                                    tma_store_2d(&tmap_c.m[d], buf, store_x, row);
+                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
+                                }
+                            }
+                            tma_store_commit();
+                        }
+                    };
                     auto pack = [&](uint32_t x0, uint32_t x1, uint32_t b2) -> uint32_t {
                         const float r0 = __uint_as_float(x0) * scale, r1 = __uint_as_float(x1) * scale;
                         if (out_bf16) {
@@ -946,6 +933,49 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         for (int g = 0; g < 2; ++g)
                             stmatrix_x4_trans(buf + st_lane + (row0 + 8 * g) * 128, pack(lo[4 * g], lo[4 * g + 1], bias2[0]), pack(lo[4 * g + 2], lo[4 * g + 3], bias2[1]),
                                               pack(hi[4 * g], hi[4 * g + 1], bias2[2]), pack(hi[4 * g + 2], hi[4 * g + 3], bias2[3]));
+                    };
+                    auto load16 = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+                        tmem_ld_16x256b_x2(frag + c, lo);
+                        tmem_ld_16x256b_x2(frag_hi + c, hi);
+                    };
+                    auto add_second = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {   // the odd k-blocks' partial sum
+                        uint32_t lo2[8], hi2[8];
+                        tmem_ld_16x256b_x2(frag + TN + c, lo2);
+                        tmem_ld_16x256b_x2(frag_hi + TN + c, hi2);
+                        tc_wait_ld();
+    #pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            lo[j] = __float_as_uint(__uint_as_float(lo[j]) + __uint_as_float(lo2[j]));
+                            hi[j] = __float_as_uint(__uint_as_float(hi[j]) + __uint_as_float(hi2[j]));
+                        }
+                    };
+                    // One bulk group per block: with two buffers the group before the last may still be reading.
+                    auto block_begin = [&]() {
+                        if (group_leader) tma_store_wait_read<C::kOutBufs - 1>();  // the stores that read this buffer are done with it
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                    };
+                    auto block_end = [&](uint32_t buf, int c0) {
+                        fence_proxy_async_smem();
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+                        if (group_leader) {
+                            // a CTA whose 128 columns all lie beyond N (second CTA of the last pair) has nothing to store
+                            int d_begin = 0, d_end = store_x < p.N ? p.n_dst : 0, row = w.tok0 + c0;
+                            if (EXT && p.scatter_rows > 0 && d_end > 0) {
+                                // row-sharded destinations: the block goes to the one buffer that owns its token rows
+                                d_begin = row / p.scatter_rows;
+                                row -= d_begin * p.scatter_rows;
+                                d_end = d_begin + 1;
+                            }
+                            for (int d = d_begin; d < d_end; ++d) {
+                                if (p.c3d) {
+                                    tma_store_3d(&tmap_c.m[d], buf, 0, row, store_x >> 6);   // both 64-column tiles at once
+                                } else {
+                                    tma_store_2d(&tmap_c.m[d], buf, store_x, row);
+                                    if (store_x + 64 < p.N) tma_store_2d(&tmap_c.m[d], buf + kOutRows * 128, store_x + 64, row);
+                                }
+                            }
+                            tma_store_commit();
+                        }
                     };
                     constexpr int kPasses = kOutRows / 16;                         // 16 token rows per pass
                     if constexpr (kIssuers == 2) {
@@ -1104,7 +1134,6 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             p.stats[13] = st_full;
             p.stats[14] = st_emit;
             p.stats[15] = st_chunks;
-            p.stats[11] = st_release;      // from accumulator-full seen to accumulator handed back
         }
         if (group_leader) tma_store_wait_all<0>();               // shared memory must outlive the stores that read it
     }

@@ -318,7 +318,7 @@ def read_stats(device):
         "mma": {"total": v[4], "wait_acc_free": v[5], "wait_tokens": v[6], "wait_weights": v[7]},
         "mma_detail": {"tok_head": v[16], "wgt_head": v[17], "tok_events": v[18], "wgt_events": v[19], "tok_max": v[20], "wgt_max": v[21], "kblocks": v[22], "issue": v[23]},
         "transform": {"total": v[8], "wait_weight_bytes": v[9], "wait_tmem_free": v[10]},
-        "epilogue": {"total": v[12], "wait_acc_full": v[13], "store_chunks": v[14], "chunks": v[15], "full_to_release": v[11]},
+        "epilogue": {"total": v[12], "wait_acc_full": v[13], "store_chunks": v[14], "chunks": v[15]},
     }
 
 
