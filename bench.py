@@ -917,15 +917,17 @@ def run_lora(args, native, hk, dev):
 
     patch = [PatchFn()]
 
+    # what `FeatherOps.Linear` does with a bf16 input: the library's cast kernel, then the fp16 kernels (the cast is timed)
     def plain():
-        return hk.scaled_mm_b200(x, bq, s, None, torch.bfloat16, torch.bfloat16)
+        return hk.scaled_mm_b200(native.bf16_to_fp16(x), bq, s, None, torch.bfloat16, torch.bfloat16)
 
     def unfused():
         return lora.apply_lora_patches(x, plain(), patch)
 
     def fused():
-        t, lb = lora.fused_lora_operands(x, patch, s)
-        return hk.scaled_mm_lora(x, bq, s, None, torch.bfloat16, torch.bfloat16, t, lb)
+        x16 = native.bf16_to_fp16(x)
+        t, lb = lora.fused_lora_operands(x16, patch, s)
+        return hk.scaled_mm_lora(x16, bq, s, None, torch.bfloat16, torch.bfloat16, t, lb)
 
     rows = {}
     for name, fn in (("linear alone", plain), ("reference sequence (linear, 2 GEMMs, add)", unfused), ("folded into the GEMM (operands prepared every call)", fused)):

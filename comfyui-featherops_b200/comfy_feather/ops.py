@@ -5,8 +5,8 @@ Same surface and behaviour as the reference's comfy_feather/ops.py:17-148 (state
 legacy `scale_weight`, exclusion rules, `convert_weight` / `set_weight` for LoRA merging, un-merged LoRA patches),
 with two differences in `forward`: the reference pads the token count up to a multiple of 16/32/64/128 with `F.pad`
 (ops.py:126-139) because its kernel needs tile-divisible M; the B200 kernel handles ragged M itself, so no padded copy
-is made and the rows beyond M never exist.  And the two dtype passes around the op (ops.py:88,103) are folded into the
-GEMM launch for fp16 / bf16 inputs.
+is made and the rows beyond M never exist.  And the cast of the result back to the model's dtype (ops.py:103) is folded
+into the GEMM's epilogue.
 """
 
 import torch
@@ -95,19 +95,19 @@ class _FeatherLinear:
         """x [M,K] any float dtype -> ([M,N] in x's dtype, whether the LoRA patches are already in it), through the
         fp16/bf16 x e5m2 kernel.
 
-        The reference casts the activations to fp16, runs the op and casts the result back (ops.py:88,103).  Here
-        both casts happen inside the GEMM launch for 16-bit inputs: bf16 activations are multiplied as they are
-        (bitwise the cast-first result for every value fp16 represents exactly; values beyond +-65504, which the
-        cast would turn into inf, are multiplied unrounded), and the epilogue stores x's dtype after rounding to
-        `out_dtype` and adding the bias in `out_dtype`, exactly the two roundings of `op(...).to(dtype)`.
+        The reference casts the activations to fp16, runs the op and casts the result back (ops.py:88,103).  Here the
+        cast back happens in the GEMM's epilogue: it stores x's dtype after rounding to `out_dtype` and adding the bias
+        in `out_dtype`, exactly the two roundings of `op(...).to(dtype)`.  bf16 activations go through the library's
+        cast kernel first (kernel/convert.py:bf16_to_fp16 in the reference: same bits as `x.to`): the GEMM can also
+        multiply bf16 activations as they are (`scaled_mm_b200` with a bf16 `a`), but its weights then have to be
+        upcast to bf16 as well, and cast + fp16 GEMM measured 6-14 % faster from 256 to 32768 tokens on the Wan shapes
+        (and is the only form the streaming kernel for a handful of tokens takes).
         """
         dtype_orig = x.dtype
         x = x.contiguous()
-        if x.dtype == torch.bfloat16 and x.is_cuda and x.shape[0] <= 16:
-            # a handful of tokens: the bandwidth-bound streaming kernel takes fp16, and the cast of M x K values is
-            # nothing (the library's cast kernel, kernel/convert.py:bf16_to_fp16 in the reference: same bits as `x.to`)
+        if x.dtype == torch.bfloat16 and x.is_cuda:
             x = bf16_to_fp16(x)
-        elif x.dtype not in (torch.float16, torch.bfloat16):
+        elif x.dtype != torch.float16:
             x = x.to(torch.float16)
         final_dtype = dtype_orig if dtype_orig in (torch.float16, torch.bfloat16) else self.out_dtype
 
