@@ -343,6 +343,23 @@ def run_ours(args):
                 events.append((e0, e1))
 
     launches_per_step = sum(lin.launches_per_call for _, lin, _, _, _ in layers)
+    if world > 1 and args.exchange == "copy_engine":
+        # If the copy-engine route cannot run on this box (the strided peer copy is refused), every rank falls back to the fused
+        # exchange together; the line then says so in `config.parallelism` and `exchange.mode`.
+        failed = 0
+        try:
+            step()
+            for _, lin, _, _, _ in layers:
+                lin.wait_exchange()
+        except native.FeatherNativeError as err:
+            failed = 1
+            print(f"[bench] copy-engine exchange unavailable on rank {rank}: {err}", file=sys.stderr, flush=True)
+        flag = torch.tensor([failed], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            args.exchange = "peer_store"
+            layers = [(a, lin.with_exchange("peer_store"), K, N, bq_full) for a, lin, K, N, bq_full in layers]
+            deferred = False
     for _ in range(args.warmup):
         step()
     native.check_device_status(dev)
